@@ -43,6 +43,7 @@ class ModelCache:
         self.call_owner: dict[int, int] = {}
         self.tensors: dict[int, dict[str, torch.Tensor]] = {}
         self.state: dict[int, torch.Tensor] = {}
+        self.named_state: dict[tuple[int, str], torch.Tensor] = {}    # states of parts that declared several
         keys: list[tuple[int, int]] = []
         for ci, (need, st, owner) in enumerate(needs):
             self.call_owner[ci] = owner
@@ -60,8 +61,15 @@ class ModelCache:
                 self.tensors[ci] = {
                     t.name: torch.zeros((self.group_pages[g] + 1, t.heads, ps, t.width), dtype=rt.dtype, device=rt.device)
                     for t in need.tensors}
-            if st is not None:
-                # one slot more than requests can hold: the sink that padded rows of a step use
+            # one slot more than requests can hold: the sink that padded rows of a step use
+            if isinstance(st, dict):
+                for name, one in st.items():
+                    t = torch.zeros((self.num_slots + 1, *one.shape), dtype=one.dtype, device=rt.device)
+                    if name:
+                        self.named_state[(ci, name)] = t
+                    else:
+                        self.state[ci] = t
+            elif st is not None:
                 self.state[ci] = torch.zeros((self.num_slots + 1, *st.shape), dtype=st.dtype, device=rt.device)
         for ci, (need, st, owner) in enumerate(needs):
             if need is not None and owner != ci:
@@ -88,6 +96,8 @@ class ModelCache:
     def reset_state(self, slot: int) -> None:
         """Zeroes the per-request state of a slot (a request starts, or starts over)."""
         for t in self.state.values():
+            t[slot].zero_()
+        for t in self.named_state.values():
             t[slot].zero_()
 
     def close(self, slot: int) -> None:
@@ -116,8 +126,8 @@ class ModelCache:
         owner = self.call_owner[call]
         return PagedView(self.tensors[owner], batch.groups[self.call_group[call]], write=(owner == call))
 
-    def state_tensor(self, call: int):
-        return self.state.get(call)
+    def state_tensor(self, call: int, name: str = ""):
+        return self.named_state.get((call, name)) if name else self.state.get(call)
 
     # ------------------------------------------------------------ metadata
     def _staging(self, n: int):

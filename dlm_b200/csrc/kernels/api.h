@@ -15,8 +15,9 @@ enum Epilogue : int {
     EPI_SWIGLU = 2    // out[m, n/2] = silu(acc[m, n]) * acc[m, n+1] for even n (interleaved weight rows)
 };
 
-// out[T, H] (f32) = table[tokens[t], :]
-void embed(const int32_t* tokens, const void* table, float* out, int T, int H, int V, int dtype, cudaStream_t stream);
+// out[T, H] (f32) = table[tokens[t], :] * scale
+void embed(const int32_t* tokens, const void* table, float* out, int T, int H, int V, float scale, int dtype,
+           cudaStream_t stream);
 
 // out[i, :] = x[rows ? rows[i] : i, :] * rsqrt(mean(x^2) + eps) * w      (x, w f32; out dtype given)
 void rmsnorm(const float* x, const float* w, void* out, const int32_t* rows, int n_rows, int H, float eps,
@@ -117,5 +118,75 @@ void reset_decode_merge_counters(cudaStream_t stream);
 // (programmatic dependent launch; on unless DLM_B200_NO_PDL=1).
 bool dep_launch_enabled();
 void set_dep_launch(bool on);
+
+// ---- learned positions, residual streams, convolutions over time, state-carrying mixers (seqmix.cu) ----
+
+// x[t, :] += table[idx[t], :]   (x f32; table of `rows` rows in `dtype`; an index outside the table sets error 6)
+void add_rows(float* x, const void* table, const int32_t* idx, int T, int H, int rows, int dtype, cudaStream_t stream);
+
+// xs[t, s, :] = x[t, :] for s < S  (both f32)
+void streams_expand(const float* x, float* xs, int T, int S, int H, cudaStream_t stream);
+// u[t, :] = sum_s a[s] xs[t, s, :] (a == nullptr: every weight 1); norm_w != nullptr: out = u / sqrt(mean(u^2) + eps)
+// * norm_w, else out = u.  xs f32 [T, S, H]; out [T, H] in out_dtype.
+void streams_reduce(const float* xs, const float* a, const float* norm_w, float eps, void* out, int T, int S, int H,
+                    int out_dtype, cudaStream_t stream);
+// xs[t, r, :] <- sum_s mix[s, r] xs[t, s, :] + outw[r] * y[t, :]  (in place, all streams from the old ones; S <= 16)
+void streams_update(float* xs, const float* mix, const float* outw, const float* y, int T, int S, int H,
+                    cudaStream_t stream);
+
+// Causal convolution over time on each channel, per request, with the request's last taps - 1 inputs carried in
+// state[slots, taps - 1, C] (f32, zero at a request's start) and brought up to date by the call:
+// out[t, c] = (add_input ? x[t, c] : 0) + bias[c] + sum_j w[c, j] x[t - taps + 1 + j, c]; act 1: silu of that.
+// x f32 with row stride ldx; w f32 [C, taps]; bias f32 [C] or nullptr; out in out_dtype with row stride ldo.
+void causal_conv(const float* x, int ldx, const float* w, const float* bias, float* state, const int32_t* cu_q,
+                 const int32_t* token_req, const int32_t* state_slot, int T, int R, int C, int taps, int add_input,
+                 int act, void* out, int ldo, int out_dtype, cudaStream_t stream);
+
+// out[r, c] = f(x[r, c]); op 0 tanh, 1 gelu (erf), 2 silu.  x f32, out in out_dtype.
+void activation(const float* x, int ldx, void* out, int ldo, int rows, int cols, int op, int out_dtype,
+                cudaStream_t stream);
+
+// ids[t, j] = table[tokens[t], j], wts[t, j] = 1 / top  (table int32 [V, top] of expert ids below E)
+void table_lookup(const int32_t* tokens, const int32_t* table, int32_t* ids, float* wts, int T, int V, int top, int E,
+                  cudaStream_t stream);
+
+// Norm over groups of `group_size` channels with a gate.  mode 0: v = y * silu(gate), out = v / rms(v) * w;
+// mode 1: out = y / rms(y) * w * sigmoid(gate).  y, gate f32 (row strides ldy, ldg), w f32 [groups * group_size].
+void gated_rmsnorm(const float* y, int ldy, const float* gate, int ldg, const float* w, void* out, int ldo, int T,
+                   int groups, int group_size, float eps, int mode, int out_dtype, cudaStream_t stream);
+
+// State-space scan.  xbc f32 rows [x: heads * P | B: groups * N | C: groups * N]; dt_raw f32 [T, heads] (row stride
+// lddt); state f32 [slots, heads, N, P]; y f32 [T, heads * P].  Per head (group = head / (heads / groups)):
+// dt = softplus(dt_raw + dt_bias); S <- exp(-exp(A_log) dt) S + dt B x^T; y = S^T C + D x.
+void ssm_scan(const float* xbc, int ldx, const float* dt_raw, int lddt, const float* dt_bias, const float* A_log,
+              const float* D, float* state, const int32_t* cu_q, const int32_t* state_slot, float* y, int R, int heads,
+              int P, int N, int groups, cudaStream_t stream);
+
+// Delta-rule scan.  proj f32 rows hold r, k, v and the raw removal rate at the given column offsets (heads * d
+// each); lw f32 [T, heads * d] the raw decay; state f32 [slots, heads, d, d] (key channel, value channel).
+// w = exp(-decay_coef * sigmoid(lw)); a = sigmoid(a_raw + a_bias); u = k / sqrt(sum k^2 + unit_eps);
+// S <- diag(w) S - (a u)(u^T S) + k v^T; o = S^T r  (o f32 [T, heads * d]).
+void delta_scan(const float* proj, int ld, int off_r, int off_k, int off_v, int off_a, const float* lw, int ldlw,
+                const float* a_bias, float* state, const int32_t* cu_q, const int32_t* state_slot, float* o, int R,
+                int heads, int d, float unit_eps, float decay_coef, cudaStream_t stream);
+
+// ---- attention through a cached latent (latent_attention.cu) ----
+
+// Per token: cq_out = rmsnorm(proj[off_q : +q_rank]) * qn_w (activation dtype); the cache row of slots[t]
+// ([rank | dr] wide, pages [pages, 1, page_size, rank + dr]) = [rmsnorm(proj[off_kv : +rank]) * kvn_w |
+// rotate(proj[off_kv + rank : +dr])].  Rotation on the first rot_dims entries, pair (i, i + rot_dims / 2).
+void latent_prep(const float* proj, int ld, int off_q, int q_rank, const float* qn_w, int off_kv, int rank,
+                 const float* kvn_w, int dr, const float* inv_freq, int rot_dims, const int32_t* positions,
+                 const int32_t* slots, float eps, void* cq_out, void* cache, int page_size, int total_pages, int T,
+                 int dtype, cudaStream_t stream);
+
+// q f32 [T, H * (dn + dr)] (per head [dn unrotated | dr to be rotated]); gate f32 [T, H] raw (or nullptr);
+// w_uk [H * dn, rank], w_uv [H * dv, rank], cache and out [T, H * dv] in `dtype`; sink f32 [H] or nullptr.
+// A query at position p sees keys j with 0 <= p - j < window (window 0: all).
+void latent_attention(const float* q, int ldq, const float* gate, int ldg, const void* w_uk, const void* w_uv,
+                      const float* sink, const void* cache, const int32_t* block_table, int table_width,
+                      const int32_t* token_req, const int32_t* positions, const float* inv_freq, int rot_dims, void* out,
+                      int T, int H, int dn, int dr, int dv, int rank, int page_size, int total_pages, int window,
+                      float scale, int dtype, cudaStream_t stream);
 
 }  // namespace dlmk

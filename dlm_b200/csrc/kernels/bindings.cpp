@@ -18,8 +18,9 @@ PYBIND11_MODULE(_dlm_kernels, m) {
     m.attr("EPI_ADD") = (int)dlmk::EPI_ADD;
     m.attr("EPI_SWIGLU") = (int)dlmk::EPI_SWIGLU;
 
-    m.def("embed", [](u64 tokens, u64 table, u64 out, int T, int H, int V, int dtype, u64 stream) {
-        dlmk::embed(ptr<const int32_t>(tokens), ptr<const void>(table), ptr<float>(out), T, H, V, dtype, st(stream));
+    m.def("embed", [](u64 tokens, u64 table, u64 out, int T, int H, int V, float scale, int dtype, u64 stream) {
+        dlmk::embed(ptr<const int32_t>(tokens), ptr<const void>(table), ptr<float>(out), T, H, V, scale, dtype,
+                    st(stream));
     });
     m.def("rmsnorm", [](u64 x, u64 w, u64 out, u64 rows, int n_rows, int H, float eps, int out_dtype, u64 stream) {
         dlmk::rmsnorm(ptr<const float>(x), ptr<const float>(w), ptr<void>(out), ptr<const int32_t>(rows), n_rows, H,
@@ -91,6 +92,70 @@ PYBIND11_MODULE(_dlm_kernels, m) {
     m.def("gather_rows", [](u64 src, u64 rows, u64 out, int n_rows, int width, int dtype, u64 stream) {
         dlmk::gather_rows(ptr<const void>(src), ptr<const int32_t>(rows), ptr<void>(out), n_rows, width, dtype,
                           st(stream));
+    });
+    m.def("add_rows", [](u64 x, u64 table, u64 idx, int T, int H, int rows, int dtype, u64 stream) {
+        dlmk::add_rows(ptr<float>(x), ptr<const void>(table), ptr<const int32_t>(idx), T, H, rows, dtype, st(stream));
+    });
+    m.def("streams_expand", [](u64 x, u64 xs, int T, int S, int H, u64 stream) {
+        dlmk::streams_expand(ptr<const float>(x), ptr<float>(xs), T, S, H, st(stream));
+    });
+    m.def("streams_reduce", [](u64 xs, u64 a, u64 norm_w, float eps, u64 out, int T, int S, int H, int out_dtype,
+                               u64 stream) {
+        dlmk::streams_reduce(ptr<const float>(xs), ptr<const float>(a), ptr<const float>(norm_w), eps, ptr<void>(out), T,
+                             S, H, out_dtype, st(stream));
+    });
+    m.def("streams_update", [](u64 xs, u64 mix, u64 outw, u64 y, int T, int S, int H, u64 stream) {
+        dlmk::streams_update(ptr<float>(xs), ptr<const float>(mix), ptr<const float>(outw), ptr<const float>(y), T, S, H,
+                             st(stream));
+    });
+    m.def("causal_conv", [](u64 x, int ldx, u64 w, u64 bias, u64 state, u64 cu_q, u64 token_req, u64 state_slot, int T,
+                            int R, int C, int taps, int add_input, int act, u64 out, int ldo, int out_dtype, u64 stream) {
+        dlmk::causal_conv(ptr<const float>(x), ldx, ptr<const float>(w), ptr<const float>(bias), ptr<float>(state),
+                          ptr<const int32_t>(cu_q), ptr<const int32_t>(token_req), ptr<const int32_t>(state_slot), T, R,
+                          C, taps, add_input, act, ptr<void>(out), ldo, out_dtype, st(stream));
+    });
+    m.def("activation", [](u64 x, int ldx, u64 out, int ldo, int rows, int cols, int op, int out_dtype, u64 stream) {
+        dlmk::activation(ptr<const float>(x), ldx, ptr<void>(out), ldo, rows, cols, op, out_dtype, st(stream));
+    });
+    m.def("table_lookup", [](u64 tokens, u64 table, u64 ids, u64 wts, int T, int V, int top, int E, u64 stream) {
+        dlmk::table_lookup(ptr<const int32_t>(tokens), ptr<const int32_t>(table), ptr<int32_t>(ids), ptr<float>(wts), T,
+                           V, top, E, st(stream));
+    });
+    m.def("gated_rmsnorm", [](u64 y, int ldy, u64 gate, int ldg, u64 w, u64 out, int ldo, int T, int groups,
+                              int group_size, float eps, int mode, int out_dtype, u64 stream) {
+        dlmk::gated_rmsnorm(ptr<const float>(y), ldy, ptr<const float>(gate), ldg, ptr<const float>(w), ptr<void>(out),
+                            ldo, T, groups, group_size, eps, mode, out_dtype, st(stream));
+    });
+    m.def("ssm_scan", [](u64 xbc, int ldx, u64 dt_raw, int lddt, u64 dt_bias, u64 A_log, u64 D, u64 state, u64 cu_q,
+                         u64 state_slot, u64 y, int R, int heads, int P, int N, int groups, u64 stream) {
+        dlmk::ssm_scan(ptr<const float>(xbc), ldx, ptr<const float>(dt_raw), lddt, ptr<const float>(dt_bias),
+                       ptr<const float>(A_log), ptr<const float>(D), ptr<float>(state), ptr<const int32_t>(cu_q),
+                       ptr<const int32_t>(state_slot), ptr<float>(y), R, heads, P, N, groups, st(stream));
+    });
+    m.def("delta_scan", [](u64 proj, int ld, int off_r, int off_k, int off_v, int off_a, u64 lw, int ldlw, u64 a_bias,
+                           u64 state, u64 cu_q, u64 state_slot, u64 o, int R, int heads, int d, float unit_eps,
+                           float decay_coef, u64 stream) {
+        dlmk::delta_scan(ptr<const float>(proj), ld, off_r, off_k, off_v, off_a, ptr<const float>(lw), ldlw,
+                         ptr<const float>(a_bias), ptr<float>(state), ptr<const int32_t>(cu_q),
+                         ptr<const int32_t>(state_slot), ptr<float>(o), R, heads, d, unit_eps, decay_coef, st(stream));
+    });
+    m.def("latent_prep", [](u64 proj, int ld, int off_q, int q_rank, u64 qn_w, int off_kv, int rank, u64 kvn_w, int dr,
+                            u64 inv_freq, int rot_dims, u64 positions, u64 slots, float eps, u64 cq_out, u64 cache,
+                            int page_size, int total_pages, int T, int dtype, u64 stream) {
+        dlmk::latent_prep(ptr<const float>(proj), ld, off_q, q_rank, ptr<const float>(qn_w), off_kv, rank,
+                          ptr<const float>(kvn_w), dr, ptr<const float>(inv_freq), rot_dims,
+                          ptr<const int32_t>(positions), ptr<const int32_t>(slots), eps, ptr<void>(cq_out),
+                          ptr<void>(cache), page_size, total_pages, T, dtype, st(stream));
+    });
+    m.def("latent_attention", [](u64 q, int ldq, u64 gate, int ldg, u64 w_uk, u64 w_uv, u64 sink, u64 cache,
+                                 u64 block_table, int table_width, u64 token_req, u64 positions, u64 inv_freq,
+                                 int rot_dims, u64 out, int T, int H, int dn, int dr, int dv, int rank, int page_size,
+                                 int total_pages, int window, float scale, int dtype, u64 stream) {
+        dlmk::latent_attention(ptr<const float>(q), ldq, ptr<const float>(gate), ldg, ptr<const void>(w_uk),
+                               ptr<const void>(w_uv), ptr<const float>(sink), ptr<const void>(cache),
+                               ptr<const int32_t>(block_table), table_width, ptr<const int32_t>(token_req),
+                               ptr<const int32_t>(positions), ptr<const float>(inv_freq), rot_dims, ptr<void>(out), T, H,
+                               dn, dr, dv, rank, page_size, total_pages, window, scale, dtype, st(stream));
     });
     m.def("take_error_flag", &dlmk::take_error_flag);
     m.def("reset_decode_merge_counters", [](u64 stream) { dlmk::reset_decode_merge_counters(st(stream)); });

@@ -59,7 +59,7 @@ namespace {
 
 template <typename T>
 __global__ void embed_kernel(const int32_t* __restrict__ tokens, const T* __restrict__ table, float* out,
-                             int H, int V, int* err) {
+                             int H, int V, float scale, int* err) {
     dep_wait();
     dep_launch_next();
     const int t = blockIdx.x;
@@ -71,7 +71,7 @@ __global__ void embed_kernel(const int32_t* __restrict__ tokens, const T* __rest
         return;
     }
     const T* row = table + (long long)tok * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_f32(row[i]);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_f32(row[i]) * scale;
 }
 
 // ---------------------------------------------------------------------- rmsnorm
@@ -388,12 +388,13 @@ __global__ void moe_combine_kernel(const float* y, const int32_t* dest,
 
 int* error_flag_ptr();
 
-void embed(const int32_t* tokens, const void* table, float* out, int T, int H, int V, int dtype, cudaStream_t stream) {
+void embed(const int32_t* tokens, const void* table, float* out, int T, int H, int V, float scale, int dtype,
+           cudaStream_t stream) {
     if (T <= 0) return;
     int* err = error_flag_ptr();
     const int threads = H >= 1024 ? 256 : 128;
-    if (dtype == F32) launch_dep(embed_kernel<float>, T, threads, 0, stream, tokens, static_cast<const float*>(table), out, H, V, err);
-    else launch_dep(embed_kernel<__nv_bfloat16>, T, threads, 0, stream, tokens, static_cast<const __nv_bfloat16*>(table), out, H, V, err);
+    if (dtype == F32) launch_dep(embed_kernel<float>, T, threads, 0, stream, tokens, static_cast<const float*>(table), out, H, V, scale, err);
+    else launch_dep(embed_kernel<__nv_bfloat16>, T, threads, 0, stream, tokens, static_cast<const __nv_bfloat16*>(table), out, H, V, scale, err);
     check_launch("embed");
 }
 

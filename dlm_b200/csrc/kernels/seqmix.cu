@@ -1,0 +1,458 @@
+// Kernels of the sequence mixers that keep a state per request instead of keys and values, and of the small
+// pieces around them: learned positions, several residual streams (hyper-connections), causal convolutions
+// over time with their carried inputs, gated group norms, the state-space scan and the delta-rule scan,
+// the table that chooses a token's experts, element-wise activations.
+//
+// Everything here is computed in 32-bit whatever the activation dtype is; only what a kernel hands to a matrix
+// product is rounded to the activation dtype.  Every result of a token depends on the tokens before it in its
+// own request only, in an order that does not depend on how the request was cut into steps.
+#include "api.h"
+#include "common.cuh"
+
+namespace dlmk {
+namespace {
+
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float softplus_f(float z) { return z > 30.0f ? z : log1pf(expf(z)); }
+__device__ __forceinline__ float gelu_erf_f(float z) { return 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f)); }
+
+template <typename T> __device__ __forceinline__ void put(void* base, long long i, float v) {
+    static_cast<T*>(base)[i] = from_f32<T>(v);
+}
+
+// --------------------------------------------------------------- learned positions
+template <typename T>
+__global__ void add_rows_kernel(float* x, const T* __restrict__ table, const int32_t* __restrict__ idx, int H, int rows,
+                                int* err) {
+    const int t = blockIdx.x;
+    const int r = idx[t];
+    if (r < 0 || r >= rows) {
+        if (threadIdx.x == 0) *err = 6;
+        return;
+    }
+    const T* row = table + (long long)r * H;
+    float* o = x + (long long)t * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] += to_f32(row[i]);
+}
+
+// ----------------------------------------------------------------- residual streams
+__global__ void streams_expand_kernel(const float* __restrict__ x, float* xs, int S, int H) {
+    const int t = blockIdx.x;
+    const float* r = x + (long long)t * H;
+    float* o = xs + (long long)t * S * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = r[i];
+        for (int s = 0; s < S; ++s) o[(long long)s * H + i] = v;
+    }
+}
+
+// u = sum_s a[s] xs[t, s, :] (a == nullptr: plain sum); with norm_w: out = u / sqrt(mean(u^2) + eps) * norm_w.
+// One block a token; u is kept in shared memory between the two passes.  The sum of squares is added in a fixed
+// order: per-thread partial sums over i = tid, tid + 256, ..., a shuffle tree per warp, the warps in order.
+template <typename TOut>
+__global__ void streams_reduce_kernel(const float* __restrict__ xs, const float* __restrict__ a,
+                                      const float* __restrict__ norm_w, float eps, TOut* out, int S, int H) {
+    extern __shared__ float su[];        // [H]
+    __shared__ float s_part[32];
+    const int t = blockIdx.x;
+    const float* r = xs + (long long)t * S * H;
+    float part = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float u = 0.f;
+        for (int s = 0; s < S; ++s) u = fmaf(a ? a[s] : 1.0f, r[(long long)s * H + i], u);
+        su[i] = u;
+        part = fmaf(u, u, part);
+    }
+    TOut* o = out + (long long)t * H;
+    if (norm_w == nullptr) {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_f32<TOut>(su[i]);
+        return;
+    }
+    const float ss = block_sum(part, s_part);
+    const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_f32<TOut>((su[i] * inv) * norm_w[i]);
+}
+
+// xs[t, r, :] <- sum_s mix[s, r] xs[t, s, :] + outw[r] * y[t, :], all streams at once from the old ones.
+constexpr int MAX_STREAMS = 16;
+__global__ void streams_update_kernel(float* xs, const float* __restrict__ mix, const float* __restrict__ outw,
+                                      const float* __restrict__ y, int S, int H) {
+    __shared__ float s_mix[MAX_STREAMS * MAX_STREAMS], s_out[MAX_STREAMS];
+    for (int i = threadIdx.x; i < S * S; i += blockDim.x) s_mix[i] = mix[i];
+    for (int i = threadIdx.x; i < S; i += blockDim.x) s_out[i] = outw[i];
+    __syncthreads();
+    const int t = blockIdx.x;
+    float* r = xs + (long long)t * S * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float old[MAX_STREAMS];
+#pragma unroll
+        for (int s = 0; s < MAX_STREAMS; ++s) old[s] = s < S ? r[(long long)s * H + i] : 0.f;
+        const float yv = y[(long long)t * H + i];
+#pragma unroll
+        for (int d = 0; d < MAX_STREAMS; ++d) {
+            if (d < S) {
+                float v = 0.f;
+#pragma unroll
+                for (int s = 0; s < MAX_STREAMS; ++s)
+                    if (s < S) v = fmaf(s_mix[s * S + d], old[s], v);
+                r[(long long)d * H + i] = fmaf(s_out[d], yv, v);
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------- causal convolution
+// out[t, c] = (add_input ? x[t, c] : 0) + bias[c] + sum_j w[c, j] * x[t - taps + 1 + j, c], optionally through silu.
+// Inputs before the first token of this step come from the request's carried inputs, state[slot, taps - 1, C]
+// (oldest first; zeros when the request starts).
+template <typename TOut>
+__global__ void causal_conv_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ w,
+                                   const float* __restrict__ bias, const float* __restrict__ state,
+                                   const int32_t* __restrict__ cu_q, const int32_t* __restrict__ token_req,
+                                   const int32_t* __restrict__ state_slot, int C, int taps, int add_input, int act,
+                                   TOut* out, int ldo) {
+    const int t = blockIdx.x;
+    const int r = token_req[t];
+    const int start = cu_q[r];
+    const long long sbase = (long long)state_slot[r] * (taps - 1) * C;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
+        float acc = bias ? bias[c] : 0.f;
+        for (int j = 0; j < taps; ++j) {
+            const int src = t - (taps - 1) + j;
+            const float v = src >= start ? x[(long long)src * ldx + c]
+                                         : state[sbase + (long long)((taps - 1) + (src - start)) * C + c];
+            acc = fmaf(w[(long long)c * taps + j], v, acc);
+        }
+        if (add_input) acc += x[(long long)t * ldx + c];
+        if (act == 1) acc = silu_f(acc);
+        out[(long long)t * ldo + c] = from_f32<TOut>(acc);
+    }
+}
+
+// The carried inputs after the step: the last taps - 1 of (old carried inputs, this step's inputs).  One thread
+// owns a (request, channel): it reads what it needs before it writes.
+constexpr int MAX_TAPS = 16;
+__global__ void conv_state_kernel(const float* __restrict__ x, int ldx, float* state, const int32_t* __restrict__ cu_q,
+                                  const int32_t* __restrict__ state_slot, int C, int taps) {
+    const int r = blockIdx.x;
+    const int start = cu_q[r], n = cu_q[r + 1] - start;
+    const int keep = taps - 1;
+    float* st = state + (long long)state_slot[r] * keep * C;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
+        float v[MAX_TAPS];
+        for (int i = 0; i < keep; ++i) {
+            const int src = n - keep + i;         // index among this step's tokens; negative: an old carried input
+            v[i] = src >= 0 ? x[(long long)(start + src) * ldx + c] : st[(long long)(keep + src) * C + c];
+        }
+        for (int i = 0; i < keep; ++i) st[(long long)i * C + c] = v[i];
+    }
+}
+
+// -------------------------------------------------------------------- activations
+template <typename TOut>
+__global__ void activation_kernel(const float* __restrict__ x, int ldx, TOut* out, int ldo, int cols, int op) {
+    const int r = blockIdx.x;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < cols; c += gridDim.y * blockDim.x) {
+        const float z = x[(long long)r * ldx + c];
+        float v;
+        switch (op) {
+            case 0: v = tanhf(z); break;
+            case 1: v = gelu_erf_f(z); break;
+            case 2: v = silu_f(z); break;
+            default: v = z; break;
+        }
+        out[(long long)r * ldo + c] = from_f32<TOut>(v);
+    }
+}
+
+// ------------------------------------------------------------ experts from a table
+__global__ void table_lookup_kernel(const int32_t* __restrict__ tokens, const int32_t* __restrict__ table, int32_t* ids,
+                                    float* wts, int T, int V, int top, int E, int* err) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= T * top) return;
+    const int t = i / top, j = i - t * top;
+    const int tok = tokens[t];
+    int e = 0;
+    if (tok < 0 || tok >= V) {
+        *err = 1;
+    } else {
+        e = table[(long long)tok * top + j];
+        if (e < 0 || e >= E) {
+            *err = 4;
+            e = 0;
+        }
+    }
+    ids[i] = e;
+    wts[i] = 1.0f / (float)top;
+}
+
+// ---------------------------------------------------------------- gated group norm
+// One block a (token, group) of `gs` channels.  mode 0: v = y * silu(gate); out = v / rms(v) * w.
+// mode 1: out = y / rms(y) * w * sigmoid(gate).  rms over the group, eps inside the root.
+template <typename TOut>
+__global__ void gated_rmsnorm_kernel(const float* __restrict__ y, int ldy, const float* __restrict__ gate, int ldg,
+                                     const float* __restrict__ w, TOut* out, int ldo, int gs, float eps, int mode) {
+    __shared__ float s_part[32];
+    const int t = blockIdx.x, g = blockIdx.y;
+    const float* yr = y + (long long)t * ldy + (long long)g * gs;
+    const float* gr = gate + (long long)t * ldg + (long long)g * gs;
+    float part = 0.f;
+    for (int i = threadIdx.x; i < gs; i += blockDim.x) {
+        const float v = mode == 0 ? yr[i] * silu_f(gr[i]) : yr[i];
+        part = fmaf(v, v, part);
+    }
+    const float ss = block_sum(part, s_part);
+    const float inv = 1.0f / sqrtf(ss / (float)gs + eps);
+    TOut* o = out + (long long)t * ldo + (long long)g * gs;
+    const float* wr = w + (long long)g * gs;
+    for (int i = threadIdx.x; i < gs; i += blockDim.x) {
+        float v;
+        if (mode == 0) v = ((yr[i] * silu_f(gr[i])) * inv) * wr[i];
+        else v = ((yr[i] * inv) * wr[i]) * sigmoid_f(gr[i]);
+        o[i] = from_f32<TOut>(v);
+    }
+}
+
+// ---------------------------------------------------------------- state-space scan
+// Per head: S <- exp(-exp(A_log) dt) S + dt B x^T (S is N x P), y = S^T C + D x, dt = softplus(dt_raw + dt_bias).
+// A block owns (head, request, a chunk of the P columns) and walks the request's tokens in order; thread p owns
+// column p of S, which lives in shared memory as [N][cols] (thread p touches bank p).  Per token the block loads
+// B, C (N each) and its x values into one of two buffers; one barrier a token.
+__global__ void ssm_scan_kernel(const float* __restrict__ xbc, int ldx, const float* __restrict__ dt_raw, int lddt,
+                                const float* __restrict__ dt_bias, const float* __restrict__ A_log,
+                                const float* __restrict__ D, float* state, const int32_t* __restrict__ cu_q,
+                                const int32_t* __restrict__ state_slot, float* y, int heads, int P, int N, int groups) {
+    extern __shared__ float sm[];
+    const int h = blockIdx.x, r = blockIdx.y;
+    const int cols = blockDim.x;
+    const int p = blockIdx.z * cols + threadIdx.x;
+    const bool live = p < P;
+    float* S = sm;                           // [N][cols]
+    float* bc = sm + (size_t)N * cols;       // [2][2 N]
+    const int g = h / (heads / groups);
+    const int inner = heads * P;
+    float* st = state + (((long long)state_slot[r] * heads + h) * N) * P;
+    if (live)
+        for (int n = 0; n < N; ++n) S[n * cols + threadIdx.x] = st[(long long)n * P + p];
+    const float a = -expf(A_log[h]), dcoef = D[h], bias = dt_bias[h];
+    const int t0 = cu_q[r], t1 = cu_q[r + 1];
+    for (int t = t0; t < t1; ++t) {
+        float* buf = bc + (size_t)((t - t0) & 1) * 2 * N;
+        const float* row = xbc + (long long)t * ldx;
+        for (int i = threadIdx.x; i < 2 * N; i += cols)
+            buf[i] = i < N ? row[inner + g * N + i] : row[inner + groups * N + g * N + (i - N)];
+        __syncthreads();
+        if (live) {
+            const float dt = softplus_f(dt_raw[(long long)t * lddt + h] + bias);
+            const float decay = expf(a * dt);
+            const float xv = row[h * P + p];
+            const float dx = dt * xv;
+            float acc = 0.f;
+            for (int n = 0; n < N; ++n) {
+                const float s = fmaf(decay, S[n * cols + threadIdx.x], dx * buf[n]);
+                S[n * cols + threadIdx.x] = s;
+                acc = fmaf(s, buf[N + n], acc);
+            }
+            y[(long long)t * inner + h * P + p] = fmaf(dcoef, xv, acc);
+        }
+    }
+    if (live)
+        for (int n = 0; n < N; ++n) st[(long long)n * P + p] = S[n * cols + threadIdx.x];
+}
+
+// ----------------------------------------------------------------- delta-rule scan
+// Per head, with key channels i and value channels j (d of each):
+//   w = exp(-exp(-1/2) sigmoid(lw)), a = sigmoid(a_raw + a_bias), u = k / sqrt(sum k^2 + 1e-6)
+//   S <- diag(w) S - (a u) (u^T S) + k v^T   (both terms read the old S);   o = S^T r
+// A block owns (head, request, a chunk of value columns); thread j owns column j of S ([d][cols] in shared
+// memory).  Per token the block loads r, k, a, w (d each) into one of two buffers; one barrier a token.
+__global__ void delta_scan_kernel(const float* __restrict__ proj, int ld, int off_r, int off_k, int off_v, int off_a,
+                                  const float* __restrict__ lw, int ldlw, const float* __restrict__ a_bias, float* state,
+                                  const int32_t* __restrict__ cu_q, const int32_t* __restrict__ state_slot, float* o,
+                                  int heads, int d, float unit_eps, float decay_coef) {
+    extern __shared__ float sm[];
+    const int h = blockIdx.x, r = blockIdx.y;
+    const int cols = blockDim.x;
+    const int j = blockIdx.z * cols + threadIdx.x;
+    const bool live = j < d;
+    float* S = sm;                           // [d][cols]
+    float* vec = sm + (size_t)d * cols;      // [2][4 d]: r, k, a, w
+    float* st = state + (((long long)state_slot[r] * heads + h) * d) * d;
+    if (live)
+        for (int i = 0; i < d; ++i) S[i * cols + threadIdx.x] = st[(long long)i * d + j];
+    const int t0 = cu_q[r], t1 = cu_q[r + 1];
+    const int hd = h * d;
+    for (int t = t0; t < t1; ++t) {
+        float* buf = vec + (size_t)((t - t0) & 1) * 4 * d;
+        const float* row = proj + (long long)t * ld;
+        for (int i = threadIdx.x; i < d; i += cols) {
+            buf[i] = row[off_r + hd + i];
+            buf[d + i] = row[off_k + hd + i];
+            buf[2 * d + i] = sigmoid_f(row[off_a + hd + i] + a_bias[hd + i]);
+            buf[3 * d + i] = expf(-decay_coef * sigmoid_f(lw[(long long)t * ldlw + hd + i]));
+        }
+        __syncthreads();
+        if (live) {
+            const float* br = buf;
+            const float* bk = buf + d;
+            const float* ba = buf + 2 * d;
+            const float* bw = buf + 3 * d;
+            float ss = 0.f;
+            for (int i = 0; i < d; ++i) ss = fmaf(bk[i], bk[i], ss);
+            const float inv = 1.0f / sqrtf(ss + unit_eps);
+            float us = 0.f;                  // u^T S, this column
+            for (int i = 0; i < d; ++i) us = fmaf(bk[i] * inv, S[i * cols + threadIdx.x], us);
+            const float vj = row[off_v + hd + j];
+            float acc = 0.f;
+            for (int i = 0; i < d; ++i) {
+                const float u = bk[i] * inv;
+                float s = bw[i] * S[i * cols + threadIdx.x];
+                s = fmaf(-(ba[i] * u), us, s);
+                s = fmaf(bk[i], vj, s);
+                S[i * cols + threadIdx.x] = s;
+                acc = fmaf(s, br[i], acc);
+            }
+            o[(long long)t * heads * d + hd + j] = acc;
+        }
+    }
+    if (live)
+        for (int i = 0; i < d; ++i) st[(long long)i * d + j] = S[i * cols + threadIdx.x];
+}
+
+int scan_cols(int width) {
+    int c = 32;
+    while (c < width && c < 128) c *= 2;
+    return c;
+}
+
+}  // namespace
+
+// ======================================================================= launchers
+void add_rows(float* x, const void* table, const int32_t* idx, int T, int H, int rows, int dtype, cudaStream_t stream) {
+    if (T <= 0) return;
+    int* err = error_flag_ptr();
+    if (dtype == F32) add_rows_kernel<float><<<T, 256, 0, stream>>>(x, static_cast<const float*>(table), idx, H, rows, err);
+    else add_rows_kernel<__nv_bfloat16><<<T, 256, 0, stream>>>(x, static_cast<const __nv_bfloat16*>(table), idx, H, rows, err);
+    check_launch("add_rows");
+}
+
+void streams_expand(const float* x, float* xs, int T, int S, int H, cudaStream_t stream) {
+    if (T <= 0) return;
+    streams_expand_kernel<<<T, 256, 0, stream>>>(x, xs, S, H);
+    check_launch("streams_expand");
+}
+
+void streams_reduce(const float* xs, const float* a, const float* norm_w, float eps, void* out, int T, int S, int H,
+                    int out_dtype, cudaStream_t stream) {
+    if (T <= 0) return;
+    DLM_CHECK(S >= 1 && H >= 1, "streams_reduce: sizes");
+    const size_t smem = (size_t)H * sizeof(float);
+    DLM_CHECK(smem <= 200 * 1024, "streams_reduce: a row does not fit in shared memory");
+    if (out_dtype == F32) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(streams_reduce_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        streams_reduce_kernel<float><<<T, 256, smem, stream>>>(xs, a, norm_w, eps, static_cast<float*>(out), S, H);
+    } else {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(streams_reduce_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        streams_reduce_kernel<__nv_bfloat16><<<T, 256, smem, stream>>>(xs, a, norm_w, eps, static_cast<__nv_bfloat16*>(out), S, H);
+    }
+    check_launch("streams_reduce");
+}
+
+void streams_update(float* xs, const float* mix, const float* outw, const float* y, int T, int S, int H,
+                    cudaStream_t stream) {
+    if (T <= 0) return;
+    DLM_CHECK(S >= 1 && S <= MAX_STREAMS, "streams_update: at most 16 residual streams");
+    streams_update_kernel<<<T, 256, 0, stream>>>(xs, mix, outw, y, S, H);
+    check_launch("streams_update");
+}
+
+void causal_conv(const float* x, int ldx, const float* w, const float* bias, float* state, const int32_t* cu_q,
+                 const int32_t* token_req, const int32_t* state_slot, int T, int R, int C, int taps, int add_input,
+                 int act, void* out, int ldo, int out_dtype, cudaStream_t stream) {
+    if (T <= 0 || R <= 0) return;
+    DLM_CHECK(taps >= 1 && taps <= MAX_TAPS, "causal_conv: 1 to 16 taps");
+    const int slices = (C + 255) / 256;
+    if (out_dtype == F32)
+        causal_conv_kernel<float><<<dim3(T, slices), 256, 0, stream>>>(x, ldx, w, bias, state, cu_q, token_req, state_slot,
+                                                                    C, taps, add_input, act, static_cast<float*>(out), ldo);
+    else
+        causal_conv_kernel<__nv_bfloat16><<<dim3(T, slices), 256, 0, stream>>>(
+            x, ldx, w, bias, state, cu_q, token_req, state_slot, C, taps, add_input, act,
+            static_cast<__nv_bfloat16*>(out), ldo);
+    check_launch("causal_conv");
+    if (taps > 1) {
+        conv_state_kernel<<<dim3(R, slices), 256, 0, stream>>>(x, ldx, state, cu_q, state_slot, C, taps);
+        check_launch("conv_state");
+    }
+}
+
+void activation(const float* x, int ldx, void* out, int ldo, int rows, int cols, int op, int out_dtype,
+                cudaStream_t stream) {
+    if (rows <= 0 || cols <= 0) return;
+    const int slices = (cols + 255) / 256 > 64 ? 64 : (cols + 255) / 256;
+    if (out_dtype == F32)
+        activation_kernel<float><<<dim3(rows, slices), 256, 0, stream>>>(x, ldx, static_cast<float*>(out), ldo, cols, op);
+    else
+        activation_kernel<__nv_bfloat16><<<dim3(rows, slices), 256, 0, stream>>>(x, ldx, static_cast<__nv_bfloat16*>(out),
+                                                                              ldo, cols, op);
+    check_launch("activation");
+}
+
+void table_lookup(const int32_t* tokens, const int32_t* table, int32_t* ids, float* wts, int T, int V, int top, int E,
+                  cudaStream_t stream) {
+    if (T <= 0) return;
+    const int n = T * top;
+    table_lookup_kernel<<<(n + 255) / 256, 256, 0, stream>>>(tokens, table, ids, wts, T, V, top, E, error_flag_ptr());
+    check_launch("table_lookup");
+}
+
+void gated_rmsnorm(const float* y, int ldy, const float* gate, int ldg, const float* w, void* out, int ldo, int T,
+                   int groups, int group_size, float eps, int mode, int out_dtype, cudaStream_t stream) {
+    if (T <= 0) return;
+    const int threads = group_size >= 256 ? 256 : (group_size >= 128 ? 128 : (group_size > 32 ? 64 : 32));
+    if (out_dtype == F32)
+        gated_rmsnorm_kernel<float><<<dim3(T, groups), threads, 0, stream>>>(y, ldy, gate, ldg, w, static_cast<float*>(out),
+                                                                          ldo, group_size, eps, mode);
+    else
+        gated_rmsnorm_kernel<__nv_bfloat16><<<dim3(T, groups), threads, 0, stream>>>(
+            y, ldy, gate, ldg, w, static_cast<__nv_bfloat16*>(out), ldo, group_size, eps, mode);
+    check_launch("gated_rmsnorm");
+}
+
+void ssm_scan(const float* xbc, int ldx, const float* dt_raw, int lddt, const float* dt_bias, const float* A_log,
+              const float* D, float* state, const int32_t* cu_q, const int32_t* state_slot, float* y, int R, int heads,
+              int P, int N, int groups, cudaStream_t stream) {
+    if (R <= 0) return;
+    DLM_CHECK(groups >= 1 && heads % groups == 0, "ssm_scan: heads must be a multiple of groups");
+    const int cols = scan_cols(P);
+    const size_t smem = ((size_t)N * cols + 4 * (size_t)N) * sizeof(float);
+    DLM_CHECK(smem <= 220 * 1024, "ssm_scan: the state of a head does not fit in shared memory");
+    static size_t allowed = 48 * 1024;
+    if (smem > allowed) {
+        cudaFuncSetAttribute(ssm_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        allowed = smem;
+    }
+    ssm_scan_kernel<<<dim3(heads, R, (P + cols - 1) / cols), cols, smem, stream>>>(
+        xbc, ldx, dt_raw, lddt, dt_bias, A_log, D, state, cu_q, state_slot, y, heads, P, N, groups);
+    check_launch("ssm_scan");
+}
+
+void delta_scan(const float* proj, int ld, int off_r, int off_k, int off_v, int off_a, const float* lw, int ldlw,
+                const float* a_bias, float* state, const int32_t* cu_q, const int32_t* state_slot, float* o, int R,
+                int heads, int d, float unit_eps, float decay_coef, cudaStream_t stream) {
+    if (R <= 0) return;
+    const int cols = scan_cols(d);
+    const size_t smem = ((size_t)d * cols + 8 * (size_t)d) * sizeof(float);
+    DLM_CHECK(smem <= 220 * 1024, "delta_scan: the state of a head does not fit in shared memory");
+    static size_t allowed = 48 * 1024;
+    if (smem > allowed) {
+        cudaFuncSetAttribute(delta_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        allowed = smem;
+    }
+    delta_scan_kernel<<<dim3(heads, R, (d + cols - 1) / cols), cols, smem, stream>>>(
+        proj, ld, off_r, off_k, off_v, off_a, lw, ldlw, a_bias, state, cu_q, state_slot, o, heads, d, unit_eps,
+        decay_coef);
+    check_launch("delta_scan");
+}
+
+}  // namespace dlmk

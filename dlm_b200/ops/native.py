@@ -101,15 +101,143 @@ class NativeOps:
         if flag:
             what = {1: "token id outside the vocabulary", 2: "cache slot outside the pool",
                     3: "a visible key has no page", 4: "expert id outside the table",
-                    5: "a wait inside a kernel ran out (copy or tensor-core pipeline)"}.get(flag, "unknown")
+                    5: "a wait inside a kernel ran out (copy or tensor-core pipeline)",
+                    6: "position outside the table of learned positions"}.get(flag, "unknown")
             raise KernelError(f"a kernel reported error {flag}: {what}")
 
     # ----------------------------------------------------------------- basic
-    def embed(self, tokens, table):
+    def embed(self, tokens, table, scale=1.0):
         T, (V, H) = tokens.numel(), table.shape
         out = torch.empty((T, H), dtype=torch.float32, device=table.device)
         self.launches += 1
-        self.k.embed(_p(tokens), _p(table), _p(out), T, H, V, _dt(table.dtype), self._stream())
+        self.k.embed(_p(tokens), _p(table), _p(out), T, H, V, float(scale), _dt(table.dtype), self._stream())
+        return out
+
+    def add_rows(self, x, table, idx):
+        """``x[t] += table[idx[t]]`` in place (x 32-bit): learned position vectors."""
+        T, H = x.shape
+        assert x.dtype == torch.float32 and table.shape[1] == H and x.is_contiguous()
+        self.launches += 1
+        self.k.add_rows(_p(x), _p(table), _p(idx), T, H, table.shape[0], _dt(table.dtype), self._stream())
+
+    # ------------------------------------------------------ residual streams
+    def streams_expand(self, x, S):
+        """``[T, H] -> [T, S, H]``: S equal copies of the residual."""
+        T, H = x.shape
+        xs = torch.empty((T, S, H), dtype=torch.float32, device=x.device)
+        self.launches += 1
+        self.k.streams_expand(_p(x), _p(xs), T, S, H, self._stream())
+        return xs
+
+    def streams_reduce(self, xs, a, norm_w, eps, out_dtype):
+        """``u = sum_s a[s] xs[:, s]`` (``a`` None: plain sum), RMS-normed with ``norm_w`` unless that is None."""
+        T, S, H = xs.shape
+        assert xs.dtype == torch.float32 and xs.is_contiguous()
+        out = torch.empty((T, H), dtype=out_dtype, device=xs.device)
+        self.launches += 1
+        self.k.streams_reduce(_p(xs), _p(a), _p(norm_w), float(eps), _p(out), T, S, H, _dt(out_dtype), self._stream())
+        return out
+
+    def streams_update(self, xs, mix, outw, y):
+        """``xs[:, r] <- sum_s mix[s, r] xs[:, s] + outw[r] * y`` in place."""
+        T, S, H = xs.shape
+        assert mix.shape == (S, S) and outw.shape == (S,) and y.shape == (T, H) and y.dtype == torch.float32
+        self.launches += 1
+        self.k.streams_update(_p(xs), _p(mix), _p(outw), _p(y), T, S, H, self._stream())
+
+    # ------------------------------------------- convolutions and recurrences
+    def causal_conv(self, x, w, bias, state, batch, add_input, silu, out_dtype):
+        """Causal convolution over time per channel and request; ``x`` is 32-bit ``[T, C]`` (may be a column
+        slice of a wider tensor), ``state`` ``[slots, taps - 1, C]`` holds each request's last inputs and is
+        brought up to date."""
+        T, C = x.shape
+        taps = w.shape[1]
+        assert x.dtype == torch.float32 and x.stride(1) == 1 and w.shape[0] == C
+        assert state.shape[1:] == (taps - 1, C) and state.dtype == torch.float32
+        out = torch.empty((T, C), dtype=out_dtype, device=x.device)
+        self.launches += 2 if taps > 1 else 1
+        self.k.causal_conv(_p(x), x.stride(0), _p(w), _p(bias), _p(state), _p(batch.cu_q), _p(batch.token_req),
+                           _p(batch.state_slot), T, batch.num_requests, C, taps, int(bool(add_input)), int(bool(silu)),
+                           _p(out), C, _dt(out_dtype), self._stream())
+        return out
+
+    _ACTS = {"tanh": 0, "gelu": 1, "silu": 2}
+
+    def activation(self, x, op, out_dtype):
+        """Element-wise ``tanh`` / ``gelu`` (erf) / ``silu`` of 32-bit ``x`` (may be a column slice)."""
+        R, C = x.shape
+        assert x.dtype == torch.float32 and x.stride(1) == 1
+        out = torch.empty((R, C), dtype=out_dtype, device=x.device)
+        self.launches += 1
+        self.k.activation(_p(x), x.stride(0), _p(out), C, R, C, self._ACTS[op], _dt(out_dtype), self._stream())
+        return out
+
+    def gated_rmsnorm(self, y, gate, w, groups, eps, mode, out_dtype):
+        """Norm over ``groups`` equal parts of the channels with a gate; ``mode`` ``"silu_before"``:
+        ``rms(y * silu(gate)) * w``; ``"sigmoid_after"``: ``rms(y) * w * sigmoid(gate)``."""
+        T, C = y.shape
+        assert C % groups == 0 and gate.shape == (T, C) and y.stride(1) == 1 and gate.stride(1) == 1
+        out = torch.empty((T, C), dtype=out_dtype, device=y.device)
+        self.launches += 1
+        self.k.gated_rmsnorm(_p(y), y.stride(0), _p(gate), gate.stride(0), _p(w), _p(out), C, T, groups, C // groups,
+                             float(eps), {"silu_before": 0, "sigmoid_after": 1}[mode], _dt(out_dtype), self._stream())
+        return out
+
+    def ssm_scan(self, xbc, dt_raw, dt_bias, A_log, D, state, batch, heads, P, N, groups):
+        """State-space scan over each request's tokens; ``state`` ``[slots, heads, N, P]`` is read and left
+        up to date.  Returns y ``[T, heads * P]`` in 32-bit."""
+        T = xbc.shape[0]
+        assert xbc.shape[1] == heads * P + 2 * groups * N and xbc.dtype == torch.float32 and xbc.stride(1) == 1
+        assert dt_raw.shape == (T, heads) and dt_raw.stride(1) == 1 and state.shape[1:] == (heads, N, P)
+        y = torch.empty((T, heads * P), dtype=torch.float32, device=xbc.device)
+        self.launches += 1
+        self.k.ssm_scan(_p(xbc), xbc.stride(0), _p(dt_raw), dt_raw.stride(0), _p(dt_bias), _p(A_log), _p(D), _p(state),
+                        _p(batch.cu_q), _p(batch.state_slot), _p(y), batch.num_requests, heads, P, N, groups,
+                        self._stream())
+        return y
+
+    def delta_scan(self, proj, offsets, lw, a_bias, state, batch, heads, d, unit_eps, decay_coef):
+        """Delta-rule scan; ``proj`` 32-bit rows hold r, k, v and the raw removal rate at column ``offsets``
+        (r, k, v, a); ``lw`` the raw decay ``[T, heads * d]``; ``state`` ``[slots, heads, d, d]``."""
+        T = proj.shape[0]
+        assert proj.dtype == torch.float32 and lw.shape == (T, heads * d) and state.shape[1:] == (heads, d, d)
+        o = torch.empty((T, heads * d), dtype=torch.float32, device=proj.device)
+        self.launches += 1
+        self.k.delta_scan(_p(proj), proj.stride(0), *[int(v) for v in offsets], _p(lw), lw.stride(0), _p(a_bias),
+                          _p(state), _p(batch.cu_q), _p(batch.state_slot), _p(o), batch.num_requests, heads, d,
+                          float(unit_eps), float(decay_coef), self._stream())
+        return o
+
+    # ------------------------------------------------------- latent attention
+    def latent_prep(self, proj, off_q, q_rank, qn_w, off_kv, rank, kvn_w, dr, inv_freq, rot_dims, positions, slots,
+                    eps, cache, out_dtype):
+        """Normalises the query latent (returned, activation dtype) and writes the token's cache row
+        ``[normalised latent | rotated key part]`` at its slot."""
+        T = proj.shape[0]
+        total_pages, one, page_size, width = cache.shape
+        assert one == 1 and width == rank + dr and cache.dtype == out_dtype and proj.dtype == torch.float32
+        cq = torch.empty((T, q_rank), dtype=out_dtype, device=proj.device)
+        self.launches += 1
+        self.k.latent_prep(_p(proj), proj.stride(0), int(off_q), int(q_rank), _p(qn_w), int(off_kv), int(rank),
+                           _p(kvn_w), int(dr), _p(inv_freq), int(rot_dims), _p(positions), _p(slots), float(eps),
+                           _p(cq), _p(cache), page_size, total_pages, T, _dt(out_dtype), self._stream())
+        return cq
+
+    def latent_attention(self, q, gate, w_uk, w_uv, sink, cache, block_table, batch, inv_freq, rot_dims, H, dn, dr,
+                         dv, rank, window, scale):
+        """Windowed attention over the cached latents with a sink and a gate per head; returns ``[T, H * dv]``
+        in the cache's dtype."""
+        T = q.shape[0]
+        total_pages, _, page_size, width = cache.shape
+        assert q.dtype == torch.float32 and q.shape[1] == H * (dn + dr) and width == rank + dr
+        assert w_uk.shape == (H * dn, rank) and w_uv.shape == (H * dv, rank) and w_uk.dtype == cache.dtype
+        out = torch.empty((T, H * dv), dtype=cache.dtype, device=q.device)
+        self.launches += 1
+        self.k.latent_attention(_p(q), q.stride(0), _p(gate), 0 if gate is None else gate.stride(0), _p(w_uk),
+                                _p(w_uv), _p(sink), _p(cache), _p(block_table), block_table.shape[1],
+                                _p(batch.token_req), _p(batch.positions), _p(inv_freq), int(rot_dims), _p(out), T, H, dn,
+                                dr, dv, rank, page_size, total_pages, int(window), float(scale), _dt(cache.dtype),
+                                self._stream())
         return out
 
     def rmsnorm(self, x, w, eps, out_dtype, rows=None):
@@ -162,6 +290,37 @@ class NativeOps:
         self._gemm(a, w_gate_up, out, M, N, K, self.k.EPI_SWIGLU, a_rows=rows, offsets=offsets, num_experts=E,
                    w_expert_stride=N * K)
         return out
+
+    def grouped_act(self, a, w_up, offsets, rows, act):
+        """``act(a[rows] · w_up[e]^T)`` for each expert's rows, in the activation dtype (``act``: see
+        ``activation``)."""
+        E, N, K = w_up.shape
+        M = rows.numel()
+        up = torch.empty((M, N), dtype=torch.float32, device=a.device)
+        if (self.fast and self.tc and a.dtype == torch.bfloat16 and 8 * M > 9 * E and K % 8 == 0
+                and a.stride(0) == K):
+            gathered = torch.empty((M, K), dtype=a.dtype, device=a.device)
+            self.launches += 1
+            self.k.gather_rows(_p(a), _p(rows), _p(gathered), M, K, _dt(a.dtype), self._stream())
+            self._gemm(gathered, w_up, up, M, N, K, self.k.EPI_STORE, offsets=offsets, num_experts=E,
+                       w_expert_stride=N * K)
+        else:
+            self._gemm(a, w_up, up, M, N, K, self.k.EPI_STORE, a_rows=rows, offsets=offsets, num_experts=E,
+                       w_expert_stride=N * K)
+        return self.activation(up, act, a.dtype)
+
+    def table_route(self, tokens, table, E):
+        """Experts of each token from a table row of its id, each weighted ``1 / top``, grouped by expert:
+        ``(ids, wts, offsets, rows, dest)`` as ``route`` gives them."""
+        T = tokens.numel()
+        V, top = table.shape
+        assert table.dtype == torch.int32 and table.is_contiguous()
+        ids = torch.empty((T, top), dtype=torch.int32, device=tokens.device)
+        wts = torch.empty((T, top), dtype=torch.float32, device=tokens.device)
+        self.launches += 1
+        self.k.table_lookup(_p(tokens), _p(table), _p(ids), _p(wts), T, V, top, E, self._stream())
+        offsets, rows, dest = self.moe_permute(ids, E)
+        return ids, wts, offsets, rows, dest
 
     def grouped_linear(self, a, w, offsets):
         E, N, K = w.shape

@@ -6,7 +6,8 @@ import math
 import torch
 
 from ..registry import build_part, register_part
-from .base import Mixer, PagedKV, ParamSpec, PartSpec, Runtime, StepContext
+from .base import CacheTensor, Mixer, PagedCache, PagedKV, ParamSpec, PartSpec, Runtime, StepContext
+from .rope import rope_inv_freqs
 
 
 class GroupedQueryAttention(Mixer):
@@ -78,4 +79,79 @@ class GroupedQueryAttention(Mixer):
         ops.linear_add(o, self.w_o, resid)
 
 
+class LatentAttention(Mixer):
+    """Softmax attention whose keys and values are projections of one cached latent per token.
+
+    ``c_q = rmsnorm(W_dq h)``, ``q = W_uq c_q`` laid out per head ``[dim plain | rot_dim rotated]``;
+    ``W_dkv h = [c_raw: kv_rank | k_rot: rot_dim]``, ``c = rmsnorm(c_raw)``; head n has key ``[W_uk,n c | k_rot]``
+    (the rotated part is shared by all heads) and value ``W_uv,n c``; score ``= (q . key) * scale``.  The
+    rotation acts on the first ``rope_dims`` entries of the rotated parts of q and k, pairs ``(i, i + rope_dims / 2)``,
+    angle ``position * base^(-2i / rope_dims)``.  A query at p sees keys j with ``0 <= p - j < window`` (None:
+    all).  The softmax's denominator also holds ``exp(sink_n)``, a learned logit per head without key or value.
+    Head n's output is multiplied by ``sigmoid(W_g h)_n``; then ``W_o``.
+
+    Only ``[c | rotated k_rot]`` is cached (one paged tensor, ``kv_rank + rot_dim`` wide).  The kernels work on
+    the latent: ``q' = W_uk,n^T q_plain`` meets c directly and the weighted sum of latents goes through
+    ``W_uv,n`` at the end, so neither keys nor values of a head are ever built."""
+
+    def __init__(self, hidden_size: int, heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int, q_rank: int,
+                 eps: float, rope_base: float, rope_dims: int | None = None, window: int | None = None,
+                 scale: float | None = None, sink: bool = True, gate: bool = True):
+        self.hidden, self.H, self.dn, self.dr, self.dv = int(hidden_size), int(heads), int(dim), int(rot_dim), int(vdim)
+        self.rank, self.q_rank, self.eps = int(kv_rank), int(q_rank), float(eps)
+        self.rope_base = float(rope_base)
+        self.rope_dims = int(rope_dims) if rope_dims is not None else self.dr
+        if self.rope_dims % 2 or not (0 <= self.rope_dims <= self.dr):
+            raise ValueError(f"rope_dims must be even and at most rot_dim, got {self.rope_dims}")
+        self.window = int(window) if window else None
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.dn + self.dr)
+        self.has_sink, self.has_gate = bool(sink), bool(gate)
+        self.w_in = self.w_uq = self.w_uk = self.w_uv = self.w_o = None
+        self.qn = self.kvn = self.sink = self._freq = None
+
+    def param_specs(self):
+        H, dn, dr, dv = self.H, self.dn, self.dr, self.dv
+        specs = [ParamSpec("dq", (self.q_rank, self.hidden)), ParamSpec("dq.norm", (self.q_rank,), init="norm"),
+                 ParamSpec("uq", (H * (dn + dr), self.q_rank)),
+                 ParamSpec("dkv", (self.rank + dr, self.hidden)), ParamSpec("dkv.norm", (self.rank,), init="norm"),
+                 ParamSpec("uk", (H * dn, self.rank)), ParamSpec("uv", (H * dv, self.rank)),
+                 ParamSpec("o", (self.hidden, H * dv))]
+        if self.has_sink:
+            specs.append(ParamSpec("sink", (H,), init="bias"))
+        if self.has_gate:
+            specs.append(ParamSpec("g", (H, self.hidden)))
+        return specs
+
+    def load(self, tensors, rt: Runtime):
+        rows = [rt.matrix(tensors["dq"]), rt.matrix(tensors["dkv"])]
+        if self.has_gate:
+            rows.append(rt.matrix(tensors["g"]))
+        self.w_in = torch.cat(rows, dim=0).contiguous()
+        self.w_uq, self.w_uk, self.w_uv = (rt.matrix(tensors[n]) for n in ("uq", "uk", "uv"))
+        self.w_o = rt.matrix(tensors["o"])
+        self.qn, self.kvn = rt.vector(tensors["dq.norm"]), rt.vector(tensors["dkv.norm"])
+        self.sink = rt.vector(tensors["sink"]) if self.has_sink else None
+        self._freq = rope_inv_freqs(self.rope_dims, self.rope_base, self.rope_dims).to(rt.device) \
+            if self.rope_dims else torch.zeros(1, device=rt.device)
+
+    def cache_need(self):
+        return PagedCache((CacheTensor("latent", 1, self.rank + self.dr),), self.window)
+
+    def forward(self, h, resid, ctx: StepContext, call: int):
+        rt, ops, b = ctx.rt, ctx.rt.ops, ctx.batch
+        view = ctx.paged(call)
+        cache = view.tensors["latent"]
+        proj = ops.linear(h, self.w_in, None, torch.float32)
+        cq = ops.latent_prep(proj, 0, self.q_rank, self.qn, self.q_rank, self.rank, self.kvn, self.dr, self._freq,
+                             self.rope_dims, b.positions, view.group.slots if view.write else None, self.eps, cache,
+                             rt.dtype)
+        q = ops.linear(cq, self.w_uq, None, torch.float32)
+        gate = proj[:, self.q_rank + self.rank + self.dr:] if self.has_gate else None
+        o = ops.latent_attention(q, gate, self.w_uk, self.w_uv, self.sink, cache, view.group.block_table, b, self._freq,
+                                 self.rope_dims, self.H, self.dn, self.dr, self.dv, self.rank, self.window or 0,
+                                 self.scale)
+        ops.linear_add(o, self.w_o, resid)
+
+
 register_part("mixer", "gqa_attention", GroupedQueryAttention)
+register_part("mixer", "latent_attention", LatentAttention)

@@ -27,11 +27,14 @@ import torch
 @dataclass(frozen=True)
 class ParamSpec:
     """One tensor a part reads.  ``init`` says how the random-weights mode draws it:
-    ``linear`` N(0, 0.02), ``bias`` N(0, 0.02), ``norm`` 1 + N(0, 0.02)."""
+    ``linear`` N(0, 0.02), ``bias`` N(0, 0.02), ``norm`` 1 + N(0, 0.02), ``eye`` identity + N(0, 0.02)
+    (a square matrix), ``ids`` an integer table whose rows hold distinct ids below ``arg`` (stored as
+    int32; every other kind is a floating-point tensor)."""
     name: str
     shape: tuple[int, ...]
     init: str = "linear"
     optional: bool = False
+    arg: int = 0
 
 
 @dataclass(frozen=True)
@@ -69,7 +72,9 @@ def PagedKV(num_kv_heads: int, head_dim: int, window: int | None = None, page_si
 
 @dataclass(frozen=True)
 class RequestState:
-    """A mixer's need for a tensor of fixed size per request (zeroed when a request starts)."""
+    """A mixer's need for a tensor of fixed size per request (zeroed when a request starts).  A part that
+    needs several returns a dict ``name -> RequestState`` from ``state_need()`` and asks for each with
+    ``ctx.state(call, name)``."""
     shape: tuple[int, ...]
     dtype: torch.dtype = torch.float32
 
@@ -98,6 +103,10 @@ class Runtime:
     def vector(self, t: torch.Tensor) -> torch.Tensor:
         """Norm weights and biases: always 32-bit (they enter 32-bit arithmetic)."""
         return t.to(device=self.device, dtype=torch.float32).contiguous()
+
+    def table(self, t: torch.Tensor) -> torch.Tensor:
+        """An integer table (ids) as int32 on the device."""
+        return t.to(device=self.device, dtype=torch.int32).contiguous()
 
 
 class Part:
@@ -146,7 +155,7 @@ class Mixer(Part):
     def cache_need(self) -> PagedCache | None:
         return None
 
-    def state_need(self) -> RequestState | None:
+    def state_need(self) -> "RequestState | dict[str, RequestState] | None":
         return None
 
     def forward(self, h: torch.Tensor, resid: torch.Tensor, ctx: "StepContext", call: int) -> None:
@@ -208,7 +217,7 @@ class StepContext:
     """What a mixer or feed-forward may ask for during a step."""
 
     def __init__(self, rt: Runtime, batch: StepBatch, paged_of_call: Callable[[int], PagedView | None],
-                 state_of_call: Callable[[int], torch.Tensor | None]):
+                 state_of_call: Callable[..., torch.Tensor | None]):
         self.rt = rt
         self.batch = batch
         self._paged = paged_of_call
@@ -220,8 +229,10 @@ class StepContext:
             raise RuntimeError(f"layer call {call} asked for paged keys/values but declared no need for them")
         return v
 
-    def state(self, call: int) -> torch.Tensor:
-        s = self._state(call)
+    def state(self, call: int, name: str = "") -> torch.Tensor:
+        """The ``[slots, *shape]`` tensor of a declared per-request state (``name``: its key when the part
+        declared several)."""
+        s = self._state(call, name) if name else self._state(call)
         if s is None:
-            raise RuntimeError(f"layer call {call} asked for per-request state but declared no need for it")
+            raise RuntimeError(f"layer call {call} asked for per-request state {name!r} but declared no need for it")
         return s

@@ -1,8 +1,12 @@
 """How a mixer, a feed-forward and their norms are arranged in one layer."""
 from __future__ import annotations
 
+from dataclasses import replace
+
 from ..registry import build_part, register_part
-from .base import Part, PartSpec, StepContext
+import torch
+
+from .base import ParamSpec, Part, PartSpec, RequestState, StepContext
 
 
 class PreNormBlock(Part):
@@ -28,7 +32,7 @@ class PreNormBlock(Part):
         out = []
         for prefix, part in self.children():
             for s in part.param_specs():
-                out.append(type(s)(prefix + s.name, s.shape, s.init, s.optional))
+                out.append(replace(s, name=prefix + s.name))
         return out
 
     def load(self, tensors, rt):
@@ -41,4 +45,105 @@ class PreNormBlock(Part):
         self.ffn.forward(self.norm2.forward(resid, rt), resid, ctx, pre_norm=self.norm2)
 
 
+class HyperConnectionBlock(Part):
+    """A pre-norm layer over S residual streams ``xs[:, s]`` instead of one.  For sublayer q (1: the mixer,
+    2: the feed-forward) with learned ``in_q[S]``, ``mix_q[S, S]`` (indexed [from, to]) and ``out_q[S]``::
+
+        u  = sum_s in_q[s] xs[:, s]
+        y  = sublayer(norm_q(u))
+        xs[:, r] <- sum_s mix_q[s, r] xs[:, s] + out_q[r] y        (all streams from the old ones)
+
+    With ``input_taps`` the mixer reads ``h + conv(h)`` instead of ``h = norm_1(u)``: a causal convolution
+    over time on every channel (weights ``[hidden, taps]``, no bias, the last tap meets the current token);
+    the last ``taps - 1`` values of h are part of a request's state.  ``ffn`` None: the layer has no second
+    sublayer.  The streams, the sums and the norms are 32-bit."""
+
+    def __init__(self, hidden_size: int, streams: int, norm1: PartSpec, mixer: PartSpec, norm2: PartSpec | None = None,
+                 ffn: PartSpec | None = None, input_taps: int | None = None, names: dict[str, str] | None = None):
+        self.hidden, self.S = int(hidden_size), int(streams)
+        self.taps = int(input_taps) if input_taps else 0
+        self.norm1 = build_part("norm", norm1)
+        self.mixer = build_part("mixer", mixer)
+        self.ffn = build_part("ffn", ffn) if ffn is not None else None
+        self.norm2 = build_part("norm", norm2) if ffn is not None else None
+        self.names = {"norm1": "norm1.", "mixer": "mixer.", "norm2": "norm2.", "ffn": "ffn.", "hc1": "hc1.",
+                      "hc2": "hc2.", "input_conv": "input_conv"}
+        if names:
+            self.names.update(names)
+        self.hc = {}            # q -> (in, mix, out)
+        self.conv_w = None
+
+    def children(self):
+        out = [(self.names["norm1"], self.norm1), (self.names["mixer"], self.mixer)]
+        if self.ffn is not None:
+            out += [(self.names["norm2"], self.norm2), (self.names["ffn"], self.ffn)]
+        return out
+
+    def _own_specs(self):
+        S = self.S
+        out = []
+        for q in ("hc1", "hc2") if self.ffn is not None else ("hc1",):
+            pre = self.names[q]
+            out += [ParamSpec(pre + "in", (S,), init="norm"), ParamSpec(pre + "out", (S,), init="norm"),
+                    ParamSpec(pre + "mix", (S, S), init="eye")]
+        if self.taps:
+            out.append(ParamSpec(self.names["input_conv"], (self.hidden, self.taps)))
+        return out
+
+    def param_specs(self):
+        out = self._own_specs()
+        for prefix, part in self.children():
+            for s in part.param_specs():
+                out.append(replace(s, name=prefix + s.name))
+        return out
+
+    def load(self, tensors, rt):
+        for prefix, part in self.children():
+            mine = {prefix + s.name for s in part.param_specs()}
+            part.load({k[len(prefix):]: v for k, v in tensors.items() if k in mine}, rt)
+        for q in ("hc1", "hc2") if self.ffn is not None else ("hc1",):
+            pre = self.names[q]
+            self.hc[q] = tuple(rt.vector(tensors[pre + n]) for n in ("in", "mix", "out"))
+        if self.taps:
+            self.conv_w = rt.vector(tensors[self.names["input_conv"]])
+
+    def state_need(self):
+        need = {}
+        m = self.mixer.state_need()
+        if isinstance(m, dict):
+            need.update(m)
+        elif m is not None:
+            need[""] = m
+        if self.taps > 1:
+            need["input_conv"] = RequestState((self.taps - 1, self.hidden))
+        return need or None
+
+    def _read(self, xs, w_in, norm, rt, out_dtype):
+        rms = norm.fusable_rms()
+        if rms is not None:
+            return rt.ops.streams_reduce(xs, w_in, rms[0], rms[1], out_dtype)
+        return norm.forward(rt.ops.streams_reduce(xs, w_in, None, 0.0, torch.float32), rt, out_dtype=out_dtype)
+
+    def forward(self, xs, ctx: StepContext, call: int):
+        rt, ops = ctx.rt, ctx.rt.ops
+        T = xs.shape[0]
+        w_in, w_mix, w_out = self.hc["hc1"]
+        if self.taps:
+            h = self._read(xs, w_in, self.norm1, rt, torch.float32)
+            state = ctx.state(call, "input_conv") if self.taps > 1 else torch.empty((0, 0, self.hidden), device=xs.device)
+            h = ops.causal_conv(h, self.conv_w, None, state, ctx.batch, True, False, rt.dtype)
+        else:
+            h = self._read(xs, w_in, self.norm1, rt, rt.dtype)
+        y = torch.zeros((T, self.hidden), dtype=torch.float32, device=xs.device)
+        self.mixer.forward(h, y, ctx, call)
+        ops.streams_update(xs, w_mix, w_out, y)
+        if self.ffn is not None:
+            w_in, w_mix, w_out = self.hc["hc2"]
+            h = self._read(xs, w_in, self.norm2, rt, rt.dtype)
+            y = torch.zeros((T, self.hidden), dtype=torch.float32, device=xs.device)
+            self.ffn.forward(h, y, ctx, pre_norm=None)
+            ops.streams_update(xs, w_mix, w_out, y)
+
+
 register_part("block", "prenorm", PreNormBlock)
+register_part("block", "hyper_connections", HyperConnectionBlock)

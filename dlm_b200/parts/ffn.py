@@ -122,5 +122,43 @@ class SoftmaxTopKMoE(FeedForward):
         ops.moe_combine(y, dest, wts, shared, gate, resid)
 
 
+class TableRoutedExperts(FeedForward):
+    """A mixture of small two-matrix experts without a router: row ``token id`` of an integer table
+    ``[vocab, top]`` names the token's experts (the entries of a row differ), each weighted ``1 / top``:
+    ``resid += (1 / top) sum_e down_e · act(up_e · h)``, no biases.  ``activation``: "gelu" (the exact, erf
+    form) or "silu".  Tensors: ``table``, ``e<i>.up`` ``[ff, hidden]``, ``e<i>.down`` ``[hidden, ff]``; at load
+    the experts are stacked ``[E, ff, hidden]`` and ``[E, hidden, ff]``."""
+
+    def __init__(self, hidden_size: int, num_experts: int, top: int, expert_size: int, vocab_size: int,
+                 activation: str = "gelu"):
+        self.hidden, self.E, self.k, self.I, self.V = (int(hidden_size), int(num_experts), int(top), int(expert_size),
+                                                      int(vocab_size))
+        if not (1 <= self.k <= self.E):
+            raise ValueError("top must be in 1..experts")
+        if activation not in ("gelu", "silu"):
+            raise ValueError(f"unknown expert activation {activation!r}")
+        self.act = activation
+        self.table = self.w_up = self.w_down = None
+
+    def param_specs(self):
+        specs = [ParamSpec("table", (self.V, self.k), init="ids", arg=self.E)]
+        for e in range(self.E):
+            specs += [ParamSpec(f"e{e}.up", (self.I, self.hidden)), ParamSpec(f"e{e}.down", (self.hidden, self.I))]
+        return specs
+
+    def load(self, tensors, rt: Runtime):
+        self.table = rt.table(tensors["table"])
+        self.w_up = torch.stack([rt.matrix(tensors[f"e{e}.up"]) for e in range(self.E)]).contiguous()
+        self.w_down = torch.stack([rt.matrix(tensors[f"e{e}.down"]) for e in range(self.E)]).contiguous()
+
+    def forward(self, h, resid, ctx: StepContext, pre_norm=None):
+        ops = ctx.rt.ops
+        _, wts, offsets, rows, dest = ops.table_route(ctx.batch.tokens, self.table, self.E)
+        act = ops.grouped_act(h, self.w_up, offsets, rows, self.act)
+        y = ops.grouped_linear(act, self.w_down, offsets)
+        ops.moe_combine(y, dest, wts, None, None, resid)
+
+
+register_part("ffn", "table_experts", TableRoutedExperts)
 register_part("ffn", "swiglu_dense", DenseSwiGLU)
 register_part("ffn", "moe_softmax_topk", SoftmaxTopKMoE)

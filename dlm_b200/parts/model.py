@@ -7,7 +7,7 @@ of writing one of its own.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass, field, replace
 
 import torch
 
@@ -34,6 +34,9 @@ class ModelSpec:
     tie_word_embeddings: bool = False    # True: the embedding is the head; False: tied iff the head is absent
     order: list[LayerCall] | None = None # None: every layer once, in index order
     embed_position: PartSpec | None = None   # a position encoding that acts on the embedded tokens
+    embed_position_prefix: str = ""          # tensor-name prefix of that encoding's own tensors (if it has any)
+    embed_scale: float = 1.0                 # the embedded tokens are multiplied by this
+    residual_streams: int | None = None      # S: blocks get ``[T, S, hidden]`` (S equal copies at the start, summed at the end)
 
 
 class WeightError(ValueError):
@@ -80,11 +83,14 @@ class DecoderModel:
     def param_specs(self) -> dict[str, ParamSpec]:
         s = self.spec
         out = {s.embed_name: ParamSpec(s.embed_name, (s.vocab_size, s.hidden_size))}
+        if self.embed_position is not None:
+            for p in self.embed_position.param_specs():
+                out[s.embed_position_prefix + p.name] = replace(p, name=s.embed_position_prefix + p.name)
         for prefix, block in zip(s.layer_prefixes, self.blocks):
             for p in block.param_specs():
-                out[prefix + p.name] = ParamSpec(prefix + p.name, p.shape, p.init, p.optional)
+                out[prefix + p.name] = replace(p, name=prefix + p.name)
         for p in self.final_norm.param_specs():
-            out[s.final_norm_prefix + p.name] = ParamSpec(s.final_norm_prefix + p.name, p.shape, p.init, p.optional)
+            out[s.final_norm_prefix + p.name] = replace(p, name=s.final_norm_prefix + p.name)
         out[s.lm_head_name] = ParamSpec(s.lm_head_name, (s.vocab_size, s.hidden_size), optional=True)
         return out
 
@@ -96,9 +102,12 @@ class DecoderModel:
         wrong, wrong_dt = [], []
         for n, (dt, shape) in available.items():
             if n in specs:
-                if tuple(shape) != tuple(specs[n].shape):
-                    wrong.append((n, shape, specs[n].shape))
-                if dt not in (torch.float32, torch.bfloat16, torch.float16, torch.float64):
+                want = tuple(specs[n].shape)      # -1: any size (the checkpoint's)
+                if len(shape) != len(want) or any(w != -1 and int(g) != w for g, w in zip(shape, want)):
+                    wrong.append((n, shape, want))
+                ok = (torch.int32, torch.int64) if specs[n].init == "ids" else \
+                    (torch.float32, torch.bfloat16, torch.float16, torch.float64)
+                if dt not in ok:
                     wrong_dt.append((n, dt))
         if missing or unexpected or wrong or wrong_dt:
             raise WeightError(sorted(missing), sorted(unexpected), wrong, wrong_dt)
@@ -112,6 +121,9 @@ class DecoderModel:
             self.lm_head = self.embed                  # an alias, not a copy
         else:
             self.lm_head = rt.matrix(get(s.lm_head_name))
+        if self.embed_position is not None:
+            mine = {s.embed_position_prefix + p.name for p in self.embed_position.param_specs()}
+            self.embed_position.load({n[len(s.embed_position_prefix):]: get(n) for n in names if n in mine}, rt)
         for prefix, block in zip(s.layer_prefixes, self.blocks):
             block.load({n[len(prefix):]: get(n) for n in names if n.startswith(prefix)}, rt)
         self.final_norm.load({n[len(s.final_norm_prefix):]: get(n) for n in names
@@ -122,9 +134,11 @@ class DecoderModel:
         """Per call of the order: (PagedCache or None, RequestState or None, owner call index)."""
         out = []
         for ci, c in enumerate(self.order):
-            mixer = self.blocks[c.layer].mixer
+            block = self.blocks[c.layer]
             owner = ci if c.reads_cache_of is None else c.reads_cache_of
-            out.append((mixer.cache_need(), mixer.state_need(), owner))
+            # a block with state of its own (beside its mixer's) says so itself
+            state = block.state_need() if hasattr(block, "state_need") else block.mixer.state_need()
+            out.append((block.mixer.cache_need(), state, owner))
         return out
 
     # ---------------------------------------------------------------- step
@@ -137,10 +151,15 @@ class DecoderModel:
             return cache.paged_view(call, batch)
 
         ctx = StepContext(rt, batch, paged, cache.state_tensor)
-        x = ops.embed(batch.tokens, self.embed)
+        s = self.spec
+        x = ops.embed(batch.tokens, self.embed, s.embed_scale) if s.embed_scale != 1.0 else ops.embed(batch.tokens, self.embed)
         if self.embed_position is not None:
             self.embed_position.on_embed(x, batch.positions, rt)
+        if s.residual_streams is not None:
+            x = ops.streams_expand(x, s.residual_streams)
         for ci, c in enumerate(self.order):
             self.blocks[c.layer].forward(x, ctx, ci)
+        if s.residual_streams is not None:
+            x = ops.streams_reduce(x, None, None, 0.0, torch.float32)
         n = self.final_norm.forward(x, rt, rows=batch.logit_rows)
         return ops.linear(n, self.lm_head, None, torch.float32)

@@ -11,15 +11,17 @@ class RMSNorm(Norm):
     """``out = (x / sqrt(mean(x^2) + eps)) * weight`` with 32-bit statistics
     (src/forward/cpu.rs:934-942); the result is stored in the activation dtype."""
 
-    def __init__(self, size: int, eps: float):
-        self.size, self.eps = int(size), float(eps)
+    def __init__(self, size: int, eps: float, param: str = "weight"):
+        """``param``: the weight tensor's name relative to the part's prefix ("" when the prefix is the
+        whole name)."""
+        self.size, self.eps, self.param = int(size), float(eps), str(param)
         self.weight: torch.Tensor | None = None
 
     def param_specs(self):
-        return [ParamSpec("weight", (self.size,), init="norm")]
+        return [ParamSpec(self.param, (self.size,), init="norm")]
 
     def load(self, tensors, rt: Runtime):
-        self.weight = rt.vector(tensors["weight"])
+        self.weight = rt.vector(tensors[self.param])
 
     def forward(self, x, rt: Runtime, rows=None, out_dtype=None):
         return rt.ops.rmsnorm(x, self.weight, self.eps, out_dtype or rt.dtype, rows)

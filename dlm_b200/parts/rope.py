@@ -4,7 +4,7 @@ from __future__ import annotations
 import torch
 
 from ..registry import register_part
-from .base import PositionEncoding, Runtime
+from .base import ParamSpec, PositionEncoding, Runtime
 
 
 def rope_inv_freqs(head_dim: int, theta: float, rotary_dim: int | None = None) -> torch.Tensor:
@@ -46,6 +46,25 @@ class NoPositionEncoding(PositionEncoding):
     """Keys and queries are used as projected."""
 
 
+class LearnedPositions(PositionEncoding):
+    """A learned vector per position, added (unscaled) to the embedded tokens: ``x[t] += table[position[t]]``.
+    Positions count from 0 in each request; one beyond the table is an error the step reports."""
+
+    def __init__(self, max_positions: int, hidden_size: int, param: str = "weight"):
+        self.n, self.hidden, self.param = int(max_positions), int(hidden_size), str(param)
+        self.table: torch.Tensor | None = None
+
+    def param_specs(self):
+        return [ParamSpec(self.param, (self.n, self.hidden))]
+
+    def load(self, tensors, rt: Runtime):
+        self.table = rt.matrix(tensors[self.param])
+
+    def on_embed(self, x, positions, rt: Runtime) -> None:
+        rt.ops.add_rows(x, self.table, positions)
+
+
+register_part("position", "learned", LearnedPositions)
 register_part("position", "rope_neox", RotaryNeoX)
 register_part("position", "rope_interleaved", RotaryInterleaved)
 register_part("position", "none", NoPositionEncoding)

@@ -28,15 +28,17 @@ def architectures() -> list[str]:
 
 
 def architecture_of(raw: dict) -> str:
-    """The registry key named by a config.json: ``architectures[0]``, else ``model_type``."""
+    """The registry key named by a config.json: ``architectures[0]``, else ``architecture``, else ``model_type``."""
     _ensure_builtin()
     archs = raw.get("architectures")
     if isinstance(archs, (list, tuple)) and archs:
         name = archs[0]
+    elif isinstance(raw.get("architecture"), str):
+        name = raw["architecture"]
     elif isinstance(raw.get("model_type"), str) and raw["model_type"] in _MODEL_TYPES:
         name = _MODEL_TYPES[raw["model_type"]]
     else:
-        raise ConfigError("config.json names no architecture (keys 'architectures' / 'model_type'); "
+        raise ConfigError("config.json names no architecture (keys 'architectures' / 'architecture' / 'model_type'); "
                           f"registered: {architectures()}")
     if name not in _ARCHITECTURES:
         raise ConfigError(f"architecture {name!r} is not registered; registered: {architectures()}")
@@ -85,4 +87,4 @@ def _ensure_builtin() -> None:
         return
     _builtin_done = True
     from . import parts  # noqa: F401  registers the built-in parts
-    from .models import qwen2_moe  # noqa: F401  registers the architecture
+    from .models import qwen2_moe, zesapel  # noqa: F401  register the architectures

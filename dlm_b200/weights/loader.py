@@ -38,7 +38,7 @@ def random_model(config, seed: int, rt: Runtime):
     def get(name):
         p = specs[name]
         return random_tensor(name, p.shape, p.init, seed, device=rt.device,
-                             dtype=store_dtype if p.init == "linear" else torch.float32)
+                             dtype=store_dtype if p.init == "linear" else torch.float32, arg=p.arg)
 
     model.load(get, names)
     return config, model

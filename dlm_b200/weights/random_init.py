@@ -49,8 +49,24 @@ def tensor_key(seed: int, name: str) -> int:
     return _s64(h ^ ((seed * _GOLDEN) & ((1 << 64) - 1)))
 
 
+def random_ids(name: str, shape, below: int, seed: int, device="cpu") -> torch.Tensor:
+    """An int32 table whose rows hold ``shape[1]`` distinct ids below ``below``: per row the ids are
+    ordered by a hash of (seed, name, row, id) and the first ones are taken."""
+    rows, top = int(shape[0]), int(shape[1])
+    if top > below:
+        raise ValueError(f"{name}: {top} distinct ids below {below} do not exist")
+    key = tensor_key(seed, name)
+    i = torch.arange(rows * below, dtype=torch.int64, device=device)
+    a = _lsr(_mix((2 * i + 1) * _s64(_GOLDEN) + key), 1).reshape(rows, below)
+    return torch.argsort(a, dim=1, stable=True)[:, :top].to(torch.int32).contiguous()
+
+
 def random_tensor(name: str, shape, init: str, seed: int, device="cpu", dtype=torch.float32,
-                  std: float = 0.02) -> torch.Tensor:
+                  std: float = 0.02, arg: int = 0) -> torch.Tensor:
+    """``arg``: for ``ids`` the number the ids stay below; for other kinds the size a ``-1`` in ``shape`` takes."""
+    if init == "ids":
+        return random_ids(name, shape, arg, seed, device)
+    shape = tuple(int(arg) if int(s) == -1 else int(s) for s in shape)
     numel = 1
     for s in shape:
         numel *= int(s)
@@ -66,7 +82,10 @@ def random_tensor(name: str, shape, init: str, seed: int, device="cpu", dtype=to
         u2 = (_lsr(b, 40).to(torch.float64) + 0.5) / float(1 << 24)
         z = torch.sqrt(-2.0 * torch.log(u1)) * torch.cos(2.0 * math.pi * u2)
         out[start:start + n] = (mean + std * z).to(dtype)
-    return out.reshape(tuple(int(s) for s in shape))
+    out = out.reshape(shape)
+    if init == "eye":
+        out += torch.eye(shape[0], shape[1], dtype=dtype, device=device)
+    return out
 
 
 def random_state_dict(param_specs: dict, seed: int, dtype=torch.float32, device="cpu",
@@ -75,7 +94,7 @@ def random_state_dict(param_specs: dict, seed: int, dtype=torch.float32, device=
     for name, p in param_specs.items():
         if name in skip or (p.optional and not include_optional):
             continue
-        out[name] = random_tensor(name, p.shape, p.init, seed, device=device, dtype=dtype)
+        out[name] = random_tensor(name, p.shape, p.init, seed, device=device, dtype=dtype, arg=p.arg)
     return out
 
 

@@ -35,8 +35,154 @@ class PlainOps:
         return _InOrder()
 
     # ----------------------------------------------------------------- basic
-    def embed(self, tokens, table):
-        return _f(table[tokens.long()])
+    def embed(self, tokens, table, scale=1.0):
+        return _f(table[tokens.long()]) * scale
+
+    def add_rows(self, x, table, idx):
+        x += _f(table[idx.long()])
+
+    # ------------------------------------------------------ residual streams
+    def streams_expand(self, x, S):
+        return x[:, None, :].repeat(1, S, 1).contiguous()
+
+    def streams_reduce(self, xs, a, norm_w, eps, out_dtype):
+        u = xs.sum(1) if a is None else torch.einsum("s,tsh->th", a, xs)
+        if norm_w is not None:
+            u = (u * (1.0 / torch.sqrt((u * u).mean(-1, keepdim=True) + eps))) * norm_w
+        return u.to(out_dtype)
+
+    def streams_update(self, xs, mix, outw, y):
+        xs.copy_(torch.einsum("sr,tsh->trh", mix, xs) + outw[None, :, None] * y[:, None, :])
+
+    # ------------------------------------------- convolutions and recurrences
+    def causal_conv(self, x, w, bias, state, batch, add_input, silu, out_dtype):
+        T, C = x.shape
+        taps = w.shape[1]
+        out = torch.zeros((T, C), dtype=torch.float32, device=x.device)
+        cu, slots = batch.cu_q.tolist(), batch.state_slot.tolist()
+        for r in range(batch.num_requests):
+            a, b = cu[r], cu[r + 1]
+            if b == a:
+                continue
+            full = torch.cat([state[slots[r]], x[a:b]], dim=0) if taps > 1 else x[a:b]   # [taps - 1 + n, C]
+            for j in range(taps):
+                out[a:b] += w[:, j] * full[j:j + (b - a)]
+            if taps > 1:
+                state[slots[r]] = full[-(taps - 1):]
+        if bias is not None:
+            out += bias
+        if add_input:
+            out += x
+        if silu:
+            out = out / (1.0 + torch.exp(-out))
+        return out.to(out_dtype)
+
+    def activation(self, x, op, out_dtype):
+        if op == "tanh":
+            v = torch.tanh(x)
+        elif op == "gelu":
+            v = 0.5 * x * (1.0 + torch.erf(x * 0.7071067811865476))
+        else:
+            v = x / (1.0 + torch.exp(-x))
+        return v.to(out_dtype)
+
+    def gated_rmsnorm(self, y, gate, w, groups, eps, mode, out_dtype):
+        T, C = y.shape
+        v = y * (gate / (1.0 + torch.exp(-gate))) if mode == "silu_before" else y
+        v = v.reshape(T, groups, C // groups)
+        v = (v * (1.0 / torch.sqrt((v * v).mean(-1, keepdim=True) + eps))).reshape(T, C) * w
+        if mode == "sigmoid_after":
+            v = v * torch.sigmoid(gate)
+        return v.to(out_dtype)
+
+    def ssm_scan(self, xbc, dt_raw, dt_bias, A_log, D, state, batch, heads, P, N, groups):
+        T = xbc.shape[0]
+        inner = heads * P
+        y = torch.zeros((T, inner), dtype=torch.float32, device=xbc.device)
+        cu, slots = batch.cu_q.tolist(), batch.state_slot.tolist()
+        dt = torch.nn.functional.softplus(dt_raw + dt_bias, threshold=30.0)
+        decay = torch.exp(-torch.exp(A_log) * dt)                     # [T, heads]
+        per = heads // groups
+        for r in range(batch.num_requests):
+            S = state[slots[r]]                                        # [heads, N, P]
+            for t in range(cu[r], cu[r + 1]):
+                x = xbc[t, :inner].reshape(heads, P)
+                B = xbc[t, inner:inner + groups * N].reshape(groups, N).repeat_interleave(per, 0)
+                C = xbc[t, inner + groups * N:].reshape(groups, N).repeat_interleave(per, 0)
+                S.copy_(decay[t][:, None, None] * S + (dt[t][:, None] * B)[:, :, None] * x[:, None, :])
+                y[t] = (torch.einsum("hnp,hn->hp", S, C) + D[:, None] * x).reshape(inner)
+        return y
+
+    def delta_scan(self, proj, offsets, lw, a_bias, state, batch, heads, d, unit_eps, decay_coef):
+        T = proj.shape[0]
+        HD = heads * d
+        o_r, o_k, o_v, o_a = offsets
+        r_, k_, v_ = (proj[:, o:o + HD].reshape(T, heads, d) for o in (o_r, o_k, o_v))
+        a_ = torch.sigmoid(proj[:, o_a:o_a + HD] + a_bias).reshape(T, heads, d)
+        w_ = torch.exp(-decay_coef * torch.sigmoid(lw)).reshape(T, heads, d)
+        u_ = k_ / torch.sqrt((k_ * k_).sum(-1, keepdim=True) + unit_eps)
+        out = torch.zeros((T, HD), dtype=torch.float32, device=proj.device)
+        cu, slots = batch.cu_q.tolist(), batch.state_slot.tolist()
+        for r in range(batch.num_requests):
+            S = state[slots[r]]                                        # [heads, d(key), d(value)]
+            for t in range(cu[r], cu[r + 1]):
+                uS = torch.einsum("hi,hij->hj", u_[t], S)
+                S.copy_(w_[t][:, :, None] * S - (a_[t] * u_[t])[:, :, None] * uS[:, None, :]
+                        + k_[t][:, :, None] * v_[t][:, None, :])
+                out[t] = torch.einsum("hij,hi->hj", S, r_[t]).reshape(HD)
+        return out
+
+    # ------------------------------------------------------- latent attention
+    @staticmethod
+    def _rotate(x, positions, inv_freq, rot_dims):
+        half = rot_dims // 2
+        if half == 0:
+            return x
+        ang = positions.to(torch.float32)[:, None] * inv_freq[None, :half]
+        while ang.dim() < x.dim():
+            ang = ang.unsqueeze(1)
+        sin, cos = torch.sin(ang), torch.cos(ang)
+        a, b = x[..., :half], x[..., half:rot_dims]
+        return torch.cat([a * cos - b * sin, b * cos + a * sin, x[..., rot_dims:]], dim=-1)
+
+    def latent_prep(self, proj, off_q, q_rank, qn_w, off_kv, rank, kvn_w, dr, inv_freq, rot_dims, positions, slots,
+                    eps, cache, out_dtype):
+        def rms(v, w):
+            return (v * (1.0 / torch.sqrt((v * v).mean(-1, keepdim=True) + eps))) * w
+        cq = rms(proj[:, off_q:off_q + q_rank], qn_w).to(out_dtype)
+        if slots is not None:
+            c = rms(proj[:, off_kv:off_kv + rank], kvn_w)
+            kr = self._rotate(proj[:, off_kv + rank:off_kv + rank + dr], positions, inv_freq, rot_dims)
+            ps = cache.shape[2]
+            sl = slots.long()
+            ok = sl >= 0
+            cache[sl[ok] // ps, 0, sl[ok] % ps, :] = torch.cat([c, kr], dim=-1)[ok].to(cache.dtype)
+        return cq
+
+    def latent_attention(self, q, gate, w_uk, w_uv, sink, cache, block_table, batch, inv_freq, rot_dims, H, dn, dr,
+                         dv, rank, window, scale):
+        T = q.shape[0]
+        ps = cache.shape[2]
+        q = q.reshape(T, H, dn + dr)
+        q_rot = self._rotate(q[..., dn:], batch.positions, inv_freq, rot_dims)
+        q_lat = torch.einsum("thd,hdr->thr", q[..., :dn], _f(w_uk).reshape(H, dn, rank))
+        out = torch.zeros((T, H, dv), dtype=torch.float32, device=q.device)
+        req, pos = batch.token_req.tolist(), batch.positions.tolist()
+        wv = _f(w_uv).reshape(H, dv, rank)
+        for t in range(T):
+            lo = max(0, pos[t] - window + 1) if window > 0 else 0
+            js = torch.arange(lo, pos[t] + 1, device=q.device)
+            pages = block_table[req[t], (js // ps).long()].long()
+            assert int(pages.min()) >= 0, "a visible key has no page"
+            rows = _f(cache[pages, 0, js % ps, :])                     # [n, rank + dr]
+            s = (q_lat[t] @ rows[:, :rank].T + q_rot[t] @ rows[:, rank:].T) * scale      # [H, n]
+            if sink is not None:
+                s = torch.cat([s, sink[:, None]], dim=1)
+            p = torch.softmax(s, dim=-1)[:, :js.numel()]
+            out[t] = torch.einsum("hr,hdr->hd", p @ rows[:, :rank], wv)
+        if gate is not None:
+            out = out * torch.sigmoid(gate)[:, :, None]
+        return out.reshape(T, H * dv).to(cache.dtype)
 
     def rmsnorm(self, x, w, eps, out_dtype, rows=None):
         if rows is not None:
@@ -71,6 +217,22 @@ class PlainOps:
                 x = _f(a[rows[off[e]:off[e + 1]].long()])
                 out[off[e]:off[e + 1]] = self._swiglu(x @ _f(w_gate_up[e]).T, a.dtype)
         return out
+
+    def grouped_act(self, a, w_up, offsets, rows, act):
+        E, N, K = w_up.shape
+        out = torch.zeros((rows.numel(), N), dtype=a.dtype, device=a.device)
+        off = offsets.tolist()
+        for e in range(E):
+            if off[e + 1] > off[e]:
+                x = _f(a[rows[off[e]:off[e + 1]].long()])
+                out[off[e]:off[e + 1]] = self.activation(x @ _f(w_up[e]).T, act, a.dtype)
+        return out
+
+    def table_route(self, tokens, table, E):
+        ids = table[tokens.long()].to(torch.int32)
+        wts = torch.full(ids.shape, 1.0 / ids.shape[1], dtype=torch.float32, device=ids.device)
+        offsets, rows, dest = self.moe_permute(ids, E)
+        return ids, wts, offsets, rows, dest
 
     def grouped_linear(self, a, w, offsets):
         E, N, K = w.shape
