@@ -27,6 +27,7 @@ def main(argv=None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (each rounded up to a page); sizes the pool")
     ap.add_argument("--page-size", type=int, default=64)
+    ap.add_argument("--slots", type=int, default=4, help="state slots: the most requests live at any time")
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
 
@@ -39,7 +40,7 @@ def main(argv=None) -> int:
     page = args.page_size
     num_pages = max(1, -(-args.max_tokens // page))
     eng = Engine.from_pretrained(args.model, dtype=args.dtype, device=args.device, page_size=page,
-                                 num_pages=num_pages, max_requests=16, max_context=max(args.max_tokens, page))
+                                 num_pages=num_pages, max_requests=args.slots, max_context=max(args.max_tokens, page))
     slots: dict[str, int] = {}
     for line in sys.stdin:
         line = line.strip()
