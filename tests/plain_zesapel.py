@@ -18,6 +18,12 @@ import torch
 
 
 # ------------------------------------------------------------------ small pieces
+def as_stored(x, rounded):
+    """What a 16-bit engine hands to a matrix product or keeps in its cache: x rounded to bfloat16 (when
+    ``rounded``), else x itself."""
+    return x.to(torch.bfloat16).to(x.dtype) if rounded else x
+
+
 def unit_rms(x, eps):
     """x / sqrt(mean(x^2) + eps) over the last dimension."""
     return x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)
@@ -69,7 +75,7 @@ def rotate_half_pairs(x, positions, base, dims):
 
 
 # ------------------------------------------------------------------------ mixers
-def mamba2(h, p, m, eps):
+def mamba2(h, p, m, eps, rounded=False):
     """State-space mixer.  m: the layer's 'mixer' dict."""
     H, P, N, G = m["heads"], m["vdim"], m["state"], m["groups"]
     inner = H * P
@@ -94,22 +100,22 @@ def mamba2(h, p, m, eps):
     y = y.reshape(T, inner) * silu(z)
     ng = m["norm_groups"]
     y = unit_rms(y.reshape(T, ng, inner // ng), eps).reshape(T, inner) * p("mix.norm")
-    return y @ p("mix.o").T
+    return as_stored(y, rounded) @ p("mix.o").T
 
 
-def latent_attention(h, p, m, eps, positions):
+def latent_attention(h, p, m, eps, positions, rounded=False):
     """Attention through a cached latent, sliding window, a sink in the softmax, an output gate."""
     H, dn, dr, dv, rank = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
     T = h.shape[0]
-    cq = rms_norm(h @ p("mix.dq").T, p("mix.dq.norm"), eps)
+    cq = as_stored(rms_norm(h @ p("mix.dq").T, p("mix.dq.norm"), eps), rounded)
     q = (cq @ p("mix.uq").T).reshape(T, H, dn + dr)
     q_plain, q_rot = q[..., :dn], q[..., dn:]
     kv = h @ p("mix.dkv").T
-    c = rms_norm(kv[:, :rank], p("mix.dkv.norm"), eps)
+    c = as_stored(rms_norm(kv[:, :rank], p("mix.dkv.norm"), eps), rounded)
     k_rot = kv[:, rank:]
     rot = m["rot"]
     q_rot = rotate_half_pairs(q_rot, positions, rot["base"], rot["dims"])
-    k_rot = rotate_half_pairs(k_rot, positions, rot["base"], rot["dims"])
+    k_rot = as_stored(rotate_half_pairs(k_rot, positions, rot["base"], rot["dims"]), rounded)
     k_plain = (c @ p("mix.uk").T).reshape(T, H, dn)
     v = (c @ p("mix.uv").T).reshape(T, H, dv)
     window = m["mask"]["size"]
@@ -125,17 +131,17 @@ def latent_attention(h, p, m, eps, positions):
             out[t, hd] = w @ v[lo:t + 1, hd]
     gate = torch.sigmoid(h @ p("mix.g").T)                       # [T, H]
     out = out * gate[:, :, None]
-    return out.reshape(T, H * dv) @ p("mix.o").T
+    return as_stored(out.reshape(T, H * dv), rounded) @ p("mix.o").T
 
 
-def general_delta(h, p, m, eps):
+def general_delta(h, p, m, eps, rounded=False):
     """Delta-rule recurrence with per-channel decay and removal rate."""
     H, d = m["heads"], m["dim"]
     T = h.shape[0]
     r = (h @ p("mix.r").T).reshape(T, H, d)
     k = (h @ p("mix.k").T).reshape(T, H, d)
     v = (h @ p("mix.v").T).reshape(T, H, d)
-    lw = torch.tanh(h @ p("mix.w1").T) @ p("mix.w2").T + p("mix.w0")
+    lw = as_stored(torch.tanh(h @ p("mix.w1").T), rounded) @ p("mix.w2").T + p("mix.w0")
     w = torch.exp(-math.exp(-0.5) * torch.sigmoid(lw)).reshape(T, H, d)
     a = torch.sigmoid(h @ p("mix.a").T + p("mix.a.b")).reshape(T, H, d)
     u = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
@@ -149,11 +155,11 @@ def general_delta(h, p, m, eps):
             o[t, hd] = S[hd].T @ r[t, hd]
     o = unit_rms(o, eps).reshape(T, H * d) * p("mix.norm")
     o = o * torch.sigmoid(h @ p("mix.g").T)
-    return o @ p("mix.o").T
+    return as_stored(o, rounded) @ p("mix.o").T
 
 
 # ------------------------------------------------------------------ feed-forward
-def table_experts(h, p, mlp, tokens):
+def table_experts(h, p, mlp, tokens, rounded=False):
     """Experts chosen by a table row of the token id, each weighted 1/top."""
     top = mlp["router"]["top"]
     table = p("mlp.table")
@@ -161,13 +167,17 @@ def table_experts(h, p, mlp, tokens):
     for t in range(h.shape[0]):
         for e in table[int(tokens[t])].tolist():
             up = p(f"mlp.e{int(e)}.up") @ h[t]
-            out[t] += (p(f"mlp.e{int(e)}.down") @ gelu_erf(up)) / top
+            out[t] += (p(f"mlp.e{int(e)}.down") @ as_stored(gelu_erf(up), rounded)) / top
     return out
 
 
 # ------------------------------------------------------------------------- model
 class PlainZesapel:
-    def __init__(self, folder_or_config, tensors=None, dtype=torch.float64):
+    def __init__(self, folder_or_config, tensors=None, dtype=torch.float64, rounded=False):
+        """``rounded``: round to bfloat16 wherever an engine that computes in bfloat16 must (what enters a matrix
+        product, what the cache keeps); everything else stays exact.  The difference to the exact result is what
+        rounding alone causes at a position."""
+        self.rounded = rounded
         if tensors is None:
             with open(os.path.join(folder_or_config, "config.json")) as f:
                 self.cfg = json.load(f)
@@ -191,20 +201,22 @@ class PlainZesapel:
             y = fn(rms_norm(u, p(f"norm{q}"), eps))
             return torch.einsum("sr,stw->rtw", p(f"hc{q}.mix"), xs) + p(f"hc{q}.out")[:, None, None] * y[None]
 
+        rd = self.rounded
+
         def mixer(h):
-            h = h + causal_conv(h, p("canon1"))
+            h = as_stored(h + causal_conv(h, p("canon1")), rd)
             kind, m = L["type"], L["mixer"]
             if kind == "mamba2":
-                return mamba2(h, p, m, eps)
+                return mamba2(h, p, m, eps, rd)
             if kind == "latent_attention":
-                return latent_attention(h, p, m, eps, positions)
+                return latent_attention(h, p, m, eps, positions, rd)
             if kind == "general_delta":
-                return general_delta(h, p, m, eps)
+                return general_delta(h, p, m, eps, rd)
             raise ValueError(kind)
 
         xs = sub(1, xs, mixer)
         if L.get("mlp") is not None:
-            xs = sub(2, xs, lambda h: table_experts(h, p, L["mlp"], tokens))
+            xs = sub(2, xs, lambda h: table_experts(as_stored(h, rd), p, L["mlp"], tokens, rd))
         return xs
 
     def forward(self, tokens, return_layers=False):
@@ -219,7 +231,7 @@ class PlainZesapel:
         for i in range(len(cfg["layers"])):
             xs = self.layer(i, xs, tokens, positions)
             after.append(xs.sum(0))
-        x = rms_norm(xs.sum(0), t["final.norm"], cfg["norm"]["eps"])
+        x = as_stored(rms_norm(xs.sum(0), t["final.norm"], cfg["norm"]["eps"]), self.rounded)
         logits = x @ t["head"].T
         return (logits, torch.stack(after)) if return_layers else logits
 
