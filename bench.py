@@ -9,6 +9,7 @@ continuous-batching workload on the windowed variant of the model (`serving`).
     python bench.py --sizes 57b             # the larger model alone as the headline
     python bench.py --workload sweep        # decode at 1k-32k tokens of context, prompts of 8k and 16k
     python bench.py --workload kernels      # the weight-streaming product alone, by shape and row length
+    python bench.py --workload zesapel      # the Zesapel design beside Qwen2-MoE at equal sizes, and its kernels alone
 
 A step is one decode step of the whole batch.  One JSON line is printed.
 """
@@ -486,6 +487,233 @@ def run_kernels(pk) -> dict:
     return out
 
 
+# ------------------------------------------------------------------ the Zesapel design beside Qwen2-MoE
+def zesapel_config(width, repeats=2, window=1024, vocab=32768, streams=4):
+    """Layer sizes that resemble a real model's: 64-wide recurrent heads, a 512-wide latent with 128 + 64-wide
+    query heads, a state of 128 per state-space head, experts as wide as the model."""
+    experts, top, ff = width // 64, 2, width
+    mlp = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff}}
+    delta = {"type": "general_delta", "mixer": {"heads": width // 64, "dim": 64}, "mlp": mlp}
+    ssm = {"type": "mamba2", "mixer": {"heads": width // 32, "vdim": 64, "state": 128, "groups": 1, "conv": 4,
+                                       "norm_groups": 1}, "mlp": mlp}
+    lat = {"type": "latent_attention", "mlp": mlp,
+           "mixer": {"heads": width // 128, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "q_rank": 768,
+                     "mask": {"size": window}, "rot": {"base": 10000.0, "dims": 64}, "scale": 192 ** -0.5}}
+    return {"architecture": "Zesapel", "vocab": vocab, "width": width, "streams": streams, "max_positions": 8192,
+            "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5}, "canon": {"taps": 4}, "layers": [delta, ssm, lat] * repeats}
+
+
+def qwen_config_like(z):
+    """Qwen2-MoE with the same width, depth, vocabulary and number of experts; as many attention heads of 128 as the
+    latent attention has; SwiGLU experts with the same number of weights as the two-matrix experts (3 I' = 2 ff)."""
+    width, layers = z["width"], len(z["layers"])
+    mlp = z["layers"][0]["mlp"]
+    inter = max(64, (2 * mlp["expert"]["ff"] // 3) // 64 * 64)
+    return dict(architectures=["Qwen2MoeForCausalLM"], model_type="qwen2_moe", num_hidden_layers=layers, hidden_size=width,
+                num_attention_heads=width // 128, num_key_value_heads=width // 128, head_dim=128,
+                num_experts=mlp["router"]["experts"], num_experts_per_tok=mlp["router"]["top"], moe_intermediate_size=inter,
+                norm_topk_prob=False, decoder_sparse_step=1, intermediate_size=4 * width, vocab_size=z["vocab"],
+                rope_theta=10000.0, rms_norm_eps=1e-5, use_sliding_window=False, tie_word_embeddings=False,
+                max_position_embeddings=8192)
+
+
+def _flush(torch, buf):
+    buf.zero_()                      # larger than L2: what the step before left there is gone
+
+
+def measure_engine(raw, batch, prompt_len, steps, prefill_tokens):
+    """Prefill tok/s of one prompt (device time of the step function) and decode tok/s of `batch` requests at
+    `prompt_len` tokens of context (device time of the replayed step), random weights, bfloat16."""
+    import torch
+
+    from dlm_b200.engine import Engine
+    from dlm_b200.registry import resolve
+    _, cfg, _ = resolve(dict(raw))
+    eng = Engine.from_random(cfg, seed=0, dtype="bfloat16", page_size=64, max_tokens=batch * (prompt_len + 512) + 8192,
+                             max_requests=batch, max_step_tokens=2048, max_context=8192)
+    gen = torch.Generator().manual_seed(0)
+    V = eng.model.spec.vocab_size
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    times = []
+    for _ in range(4):
+        s = eng.cache.open()
+        toks = torch.randint(0, V, (prefill_tokens,), generator=gen).tolist()
+        _flush(torch, flush)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        eng.step([(s, toks, [prefill_tokens - 1])])
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+        eng.cache.close(s)
+    eng.rt.ops.check_errors()
+    pre_ms = min(times[1:])
+    ids = [eng.submit(torch.randint(0, V, (prompt_len,), generator=gen).tolist(), max_new_tokens=10 ** 6) for _ in range(batch)]
+    started = set()
+    while len(started) < batch:
+        started.update(rid for rid, _ in eng.run_step())
+    for _ in range(4):
+        eng.run_step()
+    torch.cuda.synchronize()
+    ent = eng._graphs[next(k for k in eng._graphs if k[0] == batch)]
+    per = []
+    for _ in range(steps):
+        _flush(torch, flush)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        ent["graph"].replay()
+        e1.record()
+        torch.cuda.synchronize()
+        per.append(e0.elapsed_time(e1))
+    w0 = time.perf_counter()
+    produced = sum(len(eng.run_step()) for _ in range(steps))
+    torch.cuda.synchronize()
+    w1 = time.perf_counter()
+    for i in ids:
+        eng.abort(i)
+    eng.scheduler.drain_finished()
+    dec_ms = statistics.median(per)
+    out = {"prefill_tokens": prefill_tokens, "prefill_ms": round(pre_ms, 3), "prefill_tok_s": round(prefill_tokens / pre_ms * 1e3),
+           "decode_batch": batch, "decode_context": prompt_len, "decode_ms": round(dec_ms, 4),
+           "decode_tok_s": round(batch / dec_ms * 1e3), "decode_e2e_tok_s": round(produced / (w1 - w0)),
+           "launches_per_decode_step": ent["launches"]}
+    eng._graphs.clear()
+    del eng
+    import gc
+    gc.collect()
+    torch.cuda.empty_cache()
+    return out
+
+
+def zesapel_kernels(z, pk, batch, context, prefill_tokens):
+    """Each kernel of the design alone at the layer sizes of `z`: a prompt portion of `prefill_tokens` tokens of one
+    request, and a decode step of `batch` requests at `context` tokens.  Microseconds (median of 5, the cache
+    flushed before each), the bytes the kernel has to move at least, and that over time over the measured copy
+    bandwidth."""
+    import math
+    from types import SimpleNamespace
+
+    import torch
+
+    from dlm_b200.ops import native_ops
+    ops = native_ops(fast=True)
+    dev = "cuda"
+    W, S = z["width"], z["streams"]
+    md = next(L["mixer"] for L in z["layers"] if L["type"] == "general_delta")
+    ms = next(L["mixer"] for L in z["layers"] if L["type"] == "mamba2")
+    ml = next(L["mixer"] for L in z["layers"] if L["type"] == "latent_attention")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    i32 = dict(dtype=torch.int32, device=dev)
+    rows = {}
+
+    def timed(name, case, fn, nbytes):
+        ts = []
+        for _ in range(6):
+            _flush(torch, flush)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        us = statistics.median(ts[1:]) * 1e3
+        rows.setdefault(name, {})[case] = {"us": round(us, 1), "mbytes": round(nbytes / 1e6, 2),
+                                           "frac_of_copy": round(nbytes / (us * 1e-6) / 1e9 / pk["hbm_gbs"], 3)}
+
+    for case, lens, start in (("prefill", [prefill_tokens], 0), ("decode", [1] * batch, context)):
+        T, R = sum(lens), len(lens)
+        cu = [0]
+        for n in lens:
+            cu.append(cu[-1] + n)
+        b = SimpleNamespace(num_requests=R, cu_q=torch.tensor(cu, **i32), state_slot=torch.arange(R, **i32),
+                            token_req=torch.tensor([r for r, n in enumerate(lens) for _ in range(n)], **i32),
+                            positions=torch.tensor([start + i for n in lens for i in range(n)], **i32))
+        xs = torch.randn(T, S, W, device=dev)
+        a, nw, y = torch.randn(S, device=dev), torch.randn(W, device=dev), torch.randn(T, W, device=dev)
+        mix = torch.randn(S, S, device=dev)
+        timed("streams_reduce+norm", case, lambda: ops.streams_reduce(xs, a, nw, 1e-5, torch.bfloat16), T * W * (4 * S + 2))
+        timed("streams_update", case, lambda: ops.streams_update(xs, mix, a, y), T * W * 4 * (2 * S + 1))
+        taps = z["canon"]["taps"]
+        cw, cst = torch.randn(W, taps, device=dev), torch.zeros(R + 1, taps - 1, W, device=dev)
+        timed("causal_conv (mixer input)", case, lambda: ops.causal_conv(y, cw, None, cst, b, True, False, torch.bfloat16),
+              T * W * 6 + 2 * R * (taps - 1) * W * 4)
+        # state-space scan
+        H, P, N, G = ms["heads"], ms["vdim"], ms["state"], ms["groups"]
+        C = H * P + 2 * G * N
+        xbc, dt = torch.randn(T, C, device=dev), torch.randn(T, H, device=dev)
+        hb = torch.randn(H, device=dev) * 0.1
+        sst = torch.zeros(R + 1, H, N, P, device=dev)
+        timed("ssm_scan", case, lambda: ops.ssm_scan(xbc, dt, hb, hb, hb, sst, b, H, P, N, G),
+              T * (C + H + H * P) * 4 + 2 * R * H * N * P * 4)
+        z_ = torch.randn(T, H * P, device=dev)
+        nw2 = torch.randn(H * P, device=dev)
+        timed("gated_rmsnorm", case, lambda: ops.gated_rmsnorm(z_, z_, nw2, ms["norm_groups"], 1e-5, "silu_before", torch.bfloat16),
+              T * H * P * 10)
+        # delta-rule scan
+        Hd, d = md["heads"], md["dim"]
+        HD = Hd * d
+        proj, lw = torch.randn(T, 5 * HD + 16, device=dev), torch.randn(T, HD, device=dev)
+        ab = torch.zeros(HD, device=dev)
+        dst = torch.zeros(R + 1, Hd, d, d, device=dev)
+        timed("delta_scan", case, lambda: ops.delta_scan(proj, (0, HD, 2 * HD, 3 * HD), lw, ab, dst, b, Hd, d, 1e-6, math.exp(-0.5)),
+              T * HD * 6 * 4 + 2 * R * Hd * d * d * 4)
+        # latent attention over a filled cache
+        Hl, dn, dr, dv, rank, win = ml["heads"], ml["dim"], ml["rot_dim"], ml["vdim"], ml["kv_rank"], ml["mask"]["size"]
+        held = start + max(lens)
+        pages_each = -(-held // 64)
+        cache = (torch.randn(R * pages_each + 1, 1, 64, rank + dr, device=dev) * 0.3).to(torch.bfloat16)
+        table = torch.arange(R * pages_each, **i32).reshape(R, pages_each)
+        q, gate = torch.randn(T, Hl * (dn + dr), device=dev), torch.randn(T, Hl, device=dev)
+        wukT = (torch.randn(Hl, rank, dn, device=dev) * 0.05).to(torch.bfloat16)
+        wuv = (torch.randn(Hl, dv, rank, device=dev) * 0.05).to(torch.bfloat16)
+        sink = torch.zeros(Hl, device=dev)
+        freq = torch.tensor([10000.0 ** (-2.0 * i / dr) for i in range(dr // 2)], device=dev)
+        b.max_kv_len = held
+        offs = ops.head_offsets(Hl, T, dev)
+        qn, q_rot = ops.latent_q_split(q, b.positions, freq, dr, Hl, dn, dr, torch.bfloat16)
+        q_lat = ops.grouped_linear(qn.reshape(Hl * T, dn), wukT, offs).reshape(Hl, T, rank)
+        lat = ops.latent_attention(q_lat, q_rot, sink, cache, table, b, Hl, dr, rank, win, 0.07)
+        val = ops.grouped_linear(lat.reshape(Hl * T, rank), wuv, offs)
+        timed("latent_q_split", case, lambda: ops.latent_q_split(q, b.positions, freq, dr, Hl, dn, dr, torch.bfloat16),
+              T * Hl * ((dn + dr) * 4 + dn * 2 + dr * 4))
+        timed("queries through W_uk (grouped product)", case,
+              lambda: ops.grouped_linear(qn.reshape(Hl * T, dn), wukT, offs), Hl * (T * dn * 2 + rank * dn * 2 + T * rank * 4))
+        lat_bytes = (R * min(win, held) if case == "decode" else held) * (rank + dr) * 2 + T * Hl * (rank * 6 + dr * 4)
+        timed("latent_attention", case, lambda: ops.latent_attention(q_lat, q_rot, sink, cache, table, b, Hl, dr, rank, win, 0.07),
+              lat_bytes)
+        keys = sum(min(win, start + i + 1) for n in lens for i in range(n))
+        flop = 2.0 * keys * Hl * (2 * rank + dr)
+        rows["latent_attention"][case]["gflop"] = round(flop / 1e9, 2)
+        rows["latent_attention"][case]["frac_of_bf16_peak"] = round(
+            flop / (rows["latent_attention"][case]["us"] * 1e-6) / (pk["bf16_tflops"] * 1e12), 4)
+        timed("latents through W_uv (grouped product)", case,
+              lambda: ops.grouped_linear(lat.reshape(Hl * T, rank), wuv, offs), Hl * (T * rank * 2 + rank * dv * 2 + T * dv * 4))
+        timed("latent_gate_out", case, lambda: ops.latent_gate_out(val, gate, Hl, dv, torch.bfloat16), T * Hl * dv * 6)
+    ops.check_errors()
+    return rows
+
+
+def run_zesapel(args, pk) -> dict:
+    sampler = ClockSampler()
+    sampler.start()
+    t0 = time.time()
+    out = {"workload": "zesapel", "dtype": "bf16", "data": "synthetic: seeded uniform token ids, random weights N(0, 0.02)",
+           "peaks": pk, "sizes": {}, "l2": "a buffer larger than L2 is written before every timed step"}
+    for width in (1024, 2048):
+        z = zesapel_config(width)
+        q = qwen_config_like(z)
+        out["sizes"][str(width)] = {
+            "layers": len(z["layers"]), "zesapel": measure_engine(z, args.batch, args.prompt_len, args.steps, 2048),
+            "qwen2_moe": measure_engine(q, args.batch, args.prompt_len, args.steps, 2048)}
+    out["kernels_width_2048"] = zesapel_kernels(zesapel_config(2048), pk, args.batch, args.prompt_len, 2048)
+    t1 = time.time()
+    time.sleep(0.2)
+    sampler.stop()
+    out["clocks"] = sampler.summary(t0, t1)
+    return out
+
+
 def layers_that_fit(raw, want, reserve_gb=40.0):
     """As many layers of `raw` (at most `want`) as the free device memory holds beside `reserve_gb` for
     the cache pool, the head, graphs and activations."""
@@ -545,7 +773,7 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 and prefill measurements")
     ap.add_argument("--no-extras", action="store_true", help="skip `sizes_57b` and `serving`")
     ap.add_argument("--only-prefill", action="store_true", help="measure the 2,048-token prefill alone (for profiles)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "sweep", "kernels"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "sweep", "kernels", "zesapel"],
                     help="serving: the continuous-batching workload on the windowed model, instead of the default line; "
                          "sweep: decode at contexts of 1k to 32k and prefill of longer prompts, a line of its own; "
                          "kernels: the weight-streaming product alone")
@@ -575,6 +803,9 @@ def main() -> int:
         return 0
     if args.workload == "kernels":
         print(json.dumps(run_kernels(pk)))
+        return 0
+    if args.workload == "zesapel":
+        print(json.dumps(run_zesapel(args, pk)))
         return 0
     max_batch = 64 if not args.no_points else args.batch
     m = Measurement(MODEL, args.layers, args.prompt_len, args.context, max_batch, pk, page=args.page_size)

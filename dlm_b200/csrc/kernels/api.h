@@ -180,13 +180,25 @@ void latent_prep(const float* proj, int ld, int off_q, int q_rank, const float* 
                  const int32_t* slots, float eps, void* cq_out, void* cache, int page_size, int total_pages, int T,
                  int dtype, cudaStream_t stream);
 
-// q f32 [T, H * (dn + dr)] (per head [dn unrotated | dr to be rotated]); gate f32 [T, H] raw (or nullptr);
-// w_uk [H * dn, rank], w_uv [H * dv, rank], cache and out [T, H * dv] in `dtype`; sink f32 [H] or nullptr.
-// A query at position p sees keys j with 0 <= p - j < window (window 0: all).
-void latent_attention(const float* q, int ldq, const float* gate, int ldg, const void* w_uk, const void* w_uv,
-                      const float* sink, const void* cache, const int32_t* block_table, int table_width,
-                      const int32_t* token_req, const int32_t* positions, const float* inv_freq, int rot_dims, void* out,
-                      int T, int H, int dn, int dr, int dv, int rank, int page_size, int total_pages, int window,
-                      float scale, int dtype, cudaStream_t stream);
+// q f32 [T, H * (dn + dr)] (per head [dn plain | dr to be rotated]) -> qn[H, T, dn] in `dtype` (head by head: the
+// left operand of the per-head product with W_uk) and qr[T, H, dr] f32, rotated.
+void latent_q_split(const float* q, int ldq, const int32_t* positions, const float* inv_freq, int rot_dims, void* qn,
+                    float* qr, int T, int H, int dn, int dr, int dtype, cudaStream_t stream);
+// Attention over the cached latents.  q_lat f32 [H, T, rank]: the heads' queries through W_uk; q_rot f32 [T, H, dr];
+// sink f32 [H] or nullptr (a logit per head that joins the softmax's maximum and denominator only); cache
+// [pages, 1, page_size, rank + dr] and lat[H, T, rank] (the normalised weighted sums of latent rows) in `dtype`.
+// A query at position p sees keys j with 0 <= p - j < window (window 0: all).  n_splits (from
+// latent_attention_splits) > 1 cuts every token's keys over that many blocks; `partial` then holds
+// T * H * n_splits * (rank + 2) floats of scratch and a second kernel merges.
+void latent_attention(const float* q_lat, const float* q_rot, const float* sink, const void* cache,
+                      const int32_t* block_table, int table_width, const int32_t* token_req, const int32_t* positions,
+                      void* lat, float* partial, int n_splits, int T, int H, int dr, int rank, int page_size,
+                      int total_pages, int window, float scale, int dtype, cudaStream_t stream);
+// out[t, h * dv + d] = val[h * T + t, d] * sigmoid(gate[t, h]) in `dtype` (val f32 [H, T, dv]; gate f32 raw, or nullptr)
+void latent_gate_out(const float* val, const float* gate, int ldg, void* out, int T, int H, int dv, int dtype,
+                     cudaStream_t stream);
+// Splits that fill the machine for a step of T tokens whose longest visible range is max_keys (1 in 32-bit, where
+// the order of every sum is fixed).
+int latent_attention_splits(int T, int H, int max_keys, int dtype);
 
 }  // namespace dlmk

@@ -147,16 +147,26 @@ PYBIND11_MODULE(_dlm_kernels, m) {
                           ptr<const int32_t>(positions), ptr<const int32_t>(slots), eps, ptr<void>(cq_out),
                           ptr<void>(cache), page_size, total_pages, T, dtype, st(stream));
     });
-    m.def("latent_attention", [](u64 q, int ldq, u64 gate, int ldg, u64 w_uk, u64 w_uv, u64 sink, u64 cache,
-                                 u64 block_table, int table_width, u64 token_req, u64 positions, u64 inv_freq,
-                                 int rot_dims, u64 out, int T, int H, int dn, int dr, int dv, int rank, int page_size,
-                                 int total_pages, int window, float scale, int dtype, u64 stream) {
-        dlmk::latent_attention(ptr<const float>(q), ldq, ptr<const float>(gate), ldg, ptr<const void>(w_uk),
-                               ptr<const void>(w_uv), ptr<const float>(sink), ptr<const void>(cache),
-                               ptr<const int32_t>(block_table), table_width, ptr<const int32_t>(token_req),
-                               ptr<const int32_t>(positions), ptr<const float>(inv_freq), rot_dims, ptr<void>(out), T, H,
-                               dn, dr, dv, rank, page_size, total_pages, window, scale, dtype, st(stream));
+    m.def("latent_q_split", [](u64 q, int ldq, u64 positions, u64 inv_freq, int rot_dims, u64 qn, u64 qr, int T, int H,
+                               int dn, int dr, int dtype, u64 stream) {
+        dlmk::latent_q_split(ptr<const float>(q), ldq, ptr<const int32_t>(positions), ptr<const float>(inv_freq), rot_dims,
+                             ptr<void>(qn), ptr<float>(qr), T, H, dn, dr, dtype, st(stream));
     });
+    m.def("latent_gate_out", [](u64 val, u64 gate, int ldg, u64 out, int T, int H, int dv, int dtype, u64 stream) {
+        dlmk::latent_gate_out(ptr<const float>(val), ptr<const float>(gate), ldg, ptr<void>(out), T, H, dv, dtype,
+                              st(stream));
+    });
+    m.def("latent_attention", [](u64 q_lat, u64 q_rot, u64 sink, u64 cache, u64 block_table, int table_width,
+                                 u64 token_req, u64 positions, u64 lat, u64 partial, int n_splits, int T, int H, int dr,
+                                 int rank, int page_size, int total_pages, int window, float scale, int dtype,
+                                 u64 stream) {
+        dlmk::latent_attention(ptr<const float>(q_lat), ptr<const float>(q_rot), ptr<const float>(sink),
+                               ptr<const void>(cache), ptr<const int32_t>(block_table), table_width,
+                               ptr<const int32_t>(token_req), ptr<const int32_t>(positions), ptr<void>(lat),
+                               ptr<float>(partial), n_splits, T, H, dr, rank, page_size, total_pages, window, scale, dtype,
+                               st(stream));
+    });
+    m.def("latent_attention_splits", &dlmk::latent_attention_splits);
     m.def("take_error_flag", &dlmk::take_error_flag);
     m.def("reset_decode_merge_counters", [](u64 stream) { dlmk::reset_decode_merge_counters(st(stream)); });
     m.def("dep_launch_enabled", &dlmk::dep_launch_enabled);

@@ -5,9 +5,12 @@
 // a sink in the softmax's denominator (a learned logit per head without key or value), a gate on each head's
 // output.  Scores, softmax and every sum are 32-bit.
 //
-// A (token, head)'s result is computed the same way whatever else the step holds: keys are dealt to the warps
-// by their absolute position, each warp keeps a running maximum, sum and weighted latent, and the warps are
-// merged in order.
+// The two per-head products (queries through W_uk, weighted latents through W_uv) are grouped matrix products
+// with the heads as groups, outside this file; the kernels here split and rotate the queries, attend over the
+// latent rows, and gate the values.  The latent rows are shared by all heads, so a block serves a token and up to
+// eight of its heads and reads each row once.  In 32-bit a (token, head)'s result is computed in one order whatever else the step holds (keys
+// go in chunks cut at absolute positions, one after the other); in bfloat16 a step of few tokens cuts each token's
+// keys over several blocks and merges them, which changes the result by rounding only.
 #include "api.h"
 #include "common.cuh"
 
@@ -69,132 +72,269 @@ __global__ void latent_prep_kernel(const float* __restrict__ proj, int ld, int o
     }
 }
 
-constexpr int LAT_WARPS = 4;
+constexpr int LA_THREADS = 256;   // 8 warps
+constexpr int LA_KC = 32;         // keys a chunk: one per lane where a warp takes the softmax of a chunk
+constexpr int LA_HG = 8;          // most heads a block serves: the latent rows it stages are shared by all of them
 
-// One block a (token, head).  NC: latent entries a lane keeps (rank <= 32 NC).
-template <typename T, int NC>
-__global__ void latent_attention_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ gate, int ldg,
-                                        const T* __restrict__ w_uk, const T* __restrict__ w_uv,
-                                        const float* __restrict__ sink, const T* __restrict__ cache,
-                                        const int32_t* __restrict__ block_table, int table_width,
-                                        const int32_t* __restrict__ token_req, const int32_t* __restrict__ positions,
-                                        const float* __restrict__ inv_freq, int rot_dims, T* out, int H, int dn, int dr,
-                                        int dv, int rank, int page_size, int total_pages, int window, float scale,
-                                        int* err) {
-    extern __shared__ float sm[];
-    float* s_qn = sm;                         // [dn]   unrotated query part
-    float* s_qr = s_qn + dn;                  // [dr]   rotated query part
-    float* s_qa = s_qr + dr;                  // [rank] query taken through W_uk
-    float* s_acc = s_qa + rank;               // [LAT_WARPS][rank]
-    float* s_ml = s_acc + LAT_WARPS * rank;   // [LAT_WARPS][2]
-    const int t = blockIdx.x, h = blockIdx.y;
+template <typename T> struct Vec16;       // how many elements a 16-byte load brings
+template <> struct Vec16<float> { static constexpr int n = 4; };
+template <> struct Vec16<__nv_bfloat16> { static constexpr int n = 8; };
+
+// Splits the projected queries q[T, H * (dn + dr)] (per head [dn plain | dr to be rotated]): the plain parts go
+// head by head to qn[H, T, dn] in the activation dtype (the left operand of the per-head product with W_uk), the
+// rotated parts, rotated, to qr[T, H, dr] in 32-bit.
+template <typename T>
+__global__ void latent_q_split_kernel(const float* __restrict__ q, int ldq, const int32_t* __restrict__ positions,
+                                      const float* __restrict__ inv_freq, int rot_dims, T* qn, float* qr, int Tn, int H,
+                                      int dn, int dr) {
+    const int t = blockIdx.x;
+    const int half = rot_dims / 2;
+    const float pos = (float)positions[t];
+    for (int idx = threadIdx.x; idx < H * (dn + dr); idx += blockDim.x) {
+        const int h = idx / (dn + dr), i = idx - h * (dn + dr);
+        const float* row = q + (long long)t * ldq + (long long)h * (dn + dr);
+        if (i < dn) {
+            qn[((long long)h * Tn + t) * dn + i] = from_f32<T>(row[i]);
+            continue;
+        }
+        const float* r = row + dn;
+        const int e = i - dn;
+        float v;
+        if (e < half) {
+            float sn, cs;
+            sincosf(pos * inv_freq[e], &sn, &cs);
+            v = r[e] * cs - r[e + half] * sn;
+        } else if (e < 2 * half) {
+            float sn, cs;
+            sincosf(pos * inv_freq[e - half], &sn, &cs);
+            v = r[e] * cs + r[e - half] * sn;
+        } else {
+            v = r[e];
+        }
+        qr[((long long)t * H + h) * dr + e] = v;
+    }
+}
+
+// out[t, h * dv + d] = val[h * T + t, d] * sigmoid(gate[t, h])  (gate == nullptr: 1): the per-head values back
+// token by token, gated, in the activation dtype.
+template <typename T>
+__global__ void latent_gate_out_kernel(const float* __restrict__ val, const float* __restrict__ gate, int ldg, T* out,
+                                       int Tn, int H, int dv) {
+    const int t = blockIdx.x;
+    for (int idx = threadIdx.x; idx < H * dv; idx += blockDim.x) {
+        const int h = idx / dv, d = idx - h * dv;
+        const float g = gate ? 1.0f / (1.0f + expf(-gate[(long long)t * ldg + h])) : 1.0f;
+        out[(long long)t * H * dv + idx] = from_f32<T>(val[((long long)h * Tn + t) * dv + d] * g);
+    }
+}
+
+// One block a (token, group of up to LA_HG heads, split of the token's keys).  q_lat[H, T, rank] holds the heads'
+// queries already taken through W_uk, q_rot[T, H, dr] their rotated parts.  The block walks its chunks of LA_KC
+// keys (chunks are cut at absolute multiples of LA_KC, so a token's sums have one order whatever else the step
+// holds): the chunk's cache rows are staged in shared memory, every warp scores four of them against all heads,
+// warp g takes head g's softmax step over the chunk (running maximum, sum, rescale), and every thread adds the
+// chunk's rows into its columns of every head's weighted latent.  NCOL: columns of the latent a thread owns
+// (rank <= 256 NCOL).  With one split the block normalises (the sink joins the maximum and the denominator) and
+// stores lat[H, T, rank]; with more it leaves (maximum, sum, weighted latent) per head for the merge kernel.
+template <typename T, int NCOL>
+__global__ void __launch_bounds__(LA_THREADS)
+latent_attention_kernel(const float* __restrict__ q_lat, const float* __restrict__ q_rot, const float* __restrict__ sink,
+                        const T* __restrict__ cache, const int32_t* __restrict__ block_table, int table_width,
+                        const int32_t* __restrict__ token_req, const int32_t* __restrict__ positions, T* lat,
+                        float* partial, int Tn, int H, int dr, int rank, int page_size, int total_pages, int window,
+                        float scale, int hg_max, int n_splits, int* err) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int width = rank + dr;
+    const int wpad = (width + 7) & ~7;                      // row pitch of the staged keys (16-byte multiples)
+    float* s_qa = reinterpret_cast<float*>(smem_raw);       // [LA_HG][rank]  queries through W_uk
+    float* s_qr = s_qa + (size_t)LA_HG * rank;              // [LA_HG][dr]    rotated query parts
+    float* s_p = s_qr + (size_t)LA_HG * dr;                 // [LA_HG][LA_KC] scores, then weights, of a chunk
+    float* s_m = s_p + LA_HG * LA_KC;                       // [LA_HG] running maximum
+    float* s_l = s_m + LA_HG;                               // [LA_HG] running sum
+    float* s_corr = s_l + LA_HG;                            // [LA_HG] rescale of this chunk
+    T* s_keys = reinterpret_cast<T*>(s_corr + LA_HG);       // [LA_KC][wpad]
+    const int t = blockIdx.x;
+    const int h0 = blockIdx.y * hg_max;
+    const int hg = min(hg_max, H - h0);
+    const int ks = blockIdx.z;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int p = positions[t];
-    const float* qrow = q + (long long)t * ldq + (long long)h * (dn + dr);
-    for (int i = threadIdx.x; i < dn; i += blockDim.x) s_qn[i] = qrow[i];
-    {
-        const float* qr = qrow + dn;
-        const int half = rot_dims / 2;
-        const float pos = (float)p;
-        for (int i = threadIdx.x; i < dr; i += blockDim.x) {
-            float v;
-            if (i < half) {
-                float sn, cs;
-                sincosf(pos * inv_freq[i], &sn, &cs);
-                v = qr[i] * cs - qr[i + half] * sn;
-            } else if (i < 2 * half) {
-                float sn, cs;
-                sincosf(pos * inv_freq[i - half], &sn, &cs);
-                v = qr[i] * cs + qr[i - half] * sn;
-            } else {
-                v = qr[i];
-            }
-            s_qr[i] = v;
-        }
+    for (int idx = threadIdx.x; idx < hg * rank; idx += LA_THREADS) {
+        const int g = idx / rank, r = idx - g * rank;
+        s_qa[idx] = q_lat[((long long)(h0 + g) * Tn + t) * rank + r];
     }
-    __syncthreads();
-    for (int r = threadIdx.x; r < rank; r += blockDim.x) {
-        const T* wc = w_uk + (long long)h * dn * rank + r;
-        float acc = 0.f;
-        for (int d = 0; d < dn; ++d) acc = fmaf(s_qn[d], to_f32(wc[(long long)d * rank]), acc);
-        s_qa[r] = acc;
+    for (int idx = threadIdx.x; idx < hg * dr; idx += LA_THREADS) s_qr[idx] = q_rot[((long long)t * H + h0) * dr + idx];
+    if (threadIdx.x < LA_HG) {
+        s_m[threadIdx.x] = -INFINITY;
+        s_l[threadIdx.x] = 0.f;
     }
-    __syncthreads();
+    float acc[LA_HG][NCOL];
+#pragma unroll
+    for (int g = 0; g < LA_HG; ++g)
+#pragma unroll
+        for (int c = 0; c < NCOL; ++c) acc[g][c] = 0.f;
 
     const int req = token_req[t];
     const int32_t* table = block_table + (long long)req * table_width;
-    const int lo = window > 0 ? (p - window + 1 > 0 ? p - window + 1 : 0) : 0;
-    const int width = rank + dr;
-    float m = -INFINITY, l = 0.f;
-    float acc[NC];
-#pragma unroll
-    for (int n = 0; n < NC; ++n) acc[n] = 0.f;
-    // key j belongs to warp j mod LAT_WARPS
-    int j = lo + ((warp - lo) % LAT_WARPS + LAT_WARPS) % LAT_WARPS;
-    for (; j <= p; j += LAT_WARPS) {
-        const int lp = j / page_size;
-        const int page = lp < table_width ? table[lp] : -1;
-        if (page < 0 || page >= total_pages) {
-            if (lane == 0) *err = 3;
-            continue;
+    const int lo = window > 0 ? max(p - window + 1, 0) : 0;
+    const int c_first = lo / LA_KC, c_last = p / LA_KC;
+    const int per = (c_last - c_first + 1 + n_splits - 1) / n_splits;
+    const int c_begin = c_first + ks * per, c_end = min(c_begin + per, c_last + 1);
+    const bool vec = (width % Vec16<T>::n) == 0;
+    for (int ch = c_begin; ch < c_end; ++ch) {
+        __syncthreads();                                    // the chunk before is done with s_keys and s_p
+        // ---- stage the chunk's rows (zeros where the token sees no key)
+        for (int jj = warp; jj < LA_KC; jj += LA_THREADS / 32) {
+            const int j = ch * LA_KC + jj;
+            T* dst = s_keys + (size_t)jj * wpad;
+            const T* row = nullptr;
+            if (j >= lo && j <= p) {
+                const int lp = j / page_size;
+                const int page = lp < table_width ? table[lp] : -1;
+                if (page < 0 || page >= total_pages) {
+                    if (lane == 0) *err = 3;
+                } else {
+                    row = cache + ((long long)page * page_size + (j - lp * page_size)) * width;
+                }
+            }
+            if (row == nullptr) {
+                for (int i = lane; i < wpad; i += 32) dst[i] = from_f32<T>(0.f);
+            } else if (vec) {
+                const uint4* src = reinterpret_cast<const uint4*>(row);
+                uint4* d4 = reinterpret_cast<uint4*>(dst);
+                for (int i = lane; i < width / Vec16<T>::n; i += 32) d4[i] = src[i];
+            } else {
+                for (int i = lane; i < width; i += 32) dst[i] = row[i];
+            }
         }
-        const T* row = cache + ((long long)page * page_size + (j - lp * page_size)) * width;
-        float c[NC];
-        float dot = 0.f;
+        __syncthreads();
+        // ---- scores of this warp's four keys against every head
+        for (int jj = warp; jj < LA_KC; jj += LA_THREADS / 32) {
+            const int j = ch * LA_KC + jj;
+            const T* row = s_keys + (size_t)jj * wpad;
+            float kreg[8 * NCOL];
 #pragma unroll
-        for (int n = 0; n < NC; ++n) {
-            const int r = lane + 32 * n;
-            c[n] = r < rank ? to_f32(row[r]) : 0.f;
-            if (r < rank) dot = fmaf(s_qa[r], c[n], dot);
+            for (int n = 0; n < 8 * NCOL; ++n) {
+                const int r = lane + 32 * n;
+                kreg[n] = r < rank ? to_f32(row[r]) : 0.f;
+            }
+            for (int g = 0; g < hg; ++g) {
+                const float* qa = s_qa + (size_t)g * rank;
+                float dot = 0.f;
+#pragma unroll
+                for (int n = 0; n < 8 * NCOL; ++n) {
+                    const int r = lane + 32 * n;
+                    if (r < rank) dot = fmaf(qa[r], kreg[n], dot);
+                }
+                for (int i = lane; i < dr; i += 32) dot = fmaf(s_qr[g * dr + i], to_f32(row[rank + i]), dot);
+                dot = warp_sum(dot);
+                if (lane == 0) s_p[g * LA_KC + jj] = (j >= lo && j <= p) ? dot * scale : -INFINITY;
+            }
         }
-        for (int i = lane; i < dr; i += 32) dot = fmaf(s_qr[i], to_f32(row[rank + i]), dot);
-        const float sc = warp_sum(dot) * scale;
-        const float m_new = fmaxf(m, sc);
-        const float corr = expf(m - m_new);          // m = -inf at the first key: 0
-        const float pw = expf(sc - m_new);
-        l = l * corr + pw;
+        __syncthreads();
+        // ---- head g's softmax step over the chunk, by warp g
+        if (warp < hg) {
+            const float sc = s_p[warp * LA_KC + lane];
+            const float m_old = s_m[warp];
+            const float m_new = fmaxf(m_old, warp_max(sc));
+            float pw = 0.f, corr = 1.f;
+            if (m_new > -INFINITY) {
+                pw = expf(sc - m_new);                      // a key the token does not see: exp(-inf) = 0
+                corr = expf(m_old - m_new);                 // nothing before this chunk: exp(-inf) = 0
+            }
+            const float sum = warp_sum(pw);
+            s_p[warp * LA_KC + lane] = pw;
+            if (lane == 0) {
+                s_l[warp] = s_l[warp] * corr + sum;
+                s_m[warp] = m_new;
+                s_corr[warp] = corr;
+            }
+        }
+        __syncthreads();
+        // ---- weighted latents: every thread its columns, all heads
 #pragma unroll
-        for (int n = 0; n < NC; ++n) acc[n] = fmaf(pw, c[n], acc[n] * corr);
-        m = m_new;
-    }
+        for (int c = 0; c < NCOL; ++c) {
+            const int r = threadIdx.x + LA_THREADS * c;
+            if (r < rank) {
 #pragma unroll
-    for (int n = 0; n < NC; ++n) {
-        const int r = lane + 32 * n;
-        if (r < rank) s_acc[warp * rank + r] = acc[n];
-    }
-    if (lane == 0) {
-        s_ml[2 * warp] = m;
-        s_ml[2 * warp + 1] = l;
+                for (int g = 0; g < LA_HG; ++g)
+                    if (g < hg) acc[g][c] *= s_corr[g];
+                for (int jj = 0; jj < LA_KC; jj += 4) {
+                    const float k0 = to_f32(s_keys[(size_t)(jj + 0) * wpad + r]), k1 = to_f32(s_keys[(size_t)(jj + 1) * wpad + r]);
+                    const float k2 = to_f32(s_keys[(size_t)(jj + 2) * wpad + r]), k3 = to_f32(s_keys[(size_t)(jj + 3) * wpad + r]);
+#pragma unroll
+                    for (int g = 0; g < LA_HG; ++g) {
+                        if (g < hg) {
+                            const float4 pw = *reinterpret_cast<const float4*>(s_p + g * LA_KC + jj);
+                            float a = acc[g][c];
+                            a = fmaf(pw.x, k0, a);
+                            a = fmaf(pw.y, k1, a);
+                            a = fmaf(pw.z, k2, a);
+                            a = fmaf(pw.w, k3, a);
+                            acc[g][c] = a;
+                        }
+                    }
+                }
+            }
+        }
     }
     __syncthreads();
-    // merge: the sink takes part in the maximum and in the denominator, not in the sum of values
+#pragma unroll
+    for (int g = 0; g < LA_HG; ++g) {
+        if (g < hg) {
+            if (n_splits > 1) {
+                // (maximum, sum, weighted latent) of this split
+                float* dst = partial + (((long long)t * H + h0 + g) * n_splits + ks) * (rank + 2);
+                if (threadIdx.x == 0) {
+                    dst[0] = s_m[g];
+                    dst[1] = s_l[g];
+                }
+#pragma unroll
+                for (int c = 0; c < NCOL; ++c) {
+                    const int r = threadIdx.x + LA_THREADS * c;
+                    if (r < rank) dst[2 + r] = acc[g][c];
+                }
+            } else {
+                // normalise with the sink in the maximum and the denominator
+                const float snk = sink ? sink[h0 + g] : -INFINITY;
+                const float mm = fmaxf(s_m[g], snk);
+                const float f = s_l[g] > 0.f ? expf(s_m[g] - mm) : 0.f;
+                const float den = s_l[g] * f + (sink ? expf(snk - mm) : 0.f);
+                const float w = den > 0.f ? f / den : 0.f;
+                T* dst = lat + ((long long)(h0 + g) * Tn + t) * rank;
+#pragma unroll
+                for (int c = 0; c < NCOL; ++c) {
+                    const int r = threadIdx.x + LA_THREADS * c;
+                    if (r < rank) dst[r] = from_f32<T>(acc[g][c] * w);
+                }
+            }
+        }
+    }
+}
+
+// Merges the splits of a (token, head) in order and normalises as above.  One block a (token, head).
+template <typename T>
+__global__ void latent_merge_kernel(const float* __restrict__ partial, int n_splits, const float* __restrict__ sink,
+                                    T* lat, int Tn, int H, int rank) {
+    const int t = blockIdx.x, h = blockIdx.y;
+    const float* base = partial + ((long long)t * H + h) * n_splits * (rank + 2);
     const float snk = sink ? sink[h] : -INFINITY;
     float mm = snk;
-#pragma unroll
-    for (int w = 0; w < LAT_WARPS; ++w) mm = fmaxf(mm, s_ml[2 * w]);
-    float f[LAT_WARPS];
+    for (int s = 0; s < n_splits; ++s) mm = fmaxf(mm, base[(long long)s * (rank + 2)]);
     float den = sink ? expf(snk - mm) : 0.f;
-#pragma unroll
-    for (int w = 0; w < LAT_WARPS; ++w) {
-        f[w] = s_ml[2 * w + 1] > 0.f ? expf(s_ml[2 * w] - mm) : 0.f;
-        den += s_ml[2 * w + 1] * f[w];
+    for (int s = 0; s < n_splits; ++s) {
+        const float* ps = base + (long long)s * (rank + 2);
+        if (ps[1] > 0.f) den += ps[1] * expf(ps[0] - mm);
     }
     const float inv = den > 0.f ? 1.0f / den : 0.f;
-    __syncthreads();
+    T* dst = lat + ((long long)h * Tn + t) * rank;
     for (int r = threadIdx.x; r < rank; r += blockDim.x) {
         float v = 0.f;
-#pragma unroll
-        for (int w = 0; w < LAT_WARPS; ++w) v = fmaf(s_acc[w * rank + r], f[w], v);
-        s_qa[r] = v * inv;                           // the weighted latent (s_qa is free now)
-    }
-    __syncthreads();
-    const float gt = gate ? 1.0f / (1.0f + expf(-gate[(long long)t * ldg + h])) : 1.0f;
-    for (int d = warp; d < dv; d += LAT_WARPS) {
-        const T* wr = w_uv + ((long long)h * dv + d) * rank;
-        float a = 0.f;
-        for (int r = lane; r < rank; r += 32) a = fmaf(to_f32(wr[r]), s_qa[r], a);
-        a = warp_sum(a);
-        if (lane == 0) out[(long long)t * H * dv + (long long)h * dv + d] = from_f32<T>(a * gt);
+        for (int s = 0; s < n_splits; ++s) {
+            const float* ps = base + (long long)s * (rank + 2);
+            if (ps[1] > 0.f) v = fmaf(ps[2 + r], expf(ps[0] - mm), v);
+        }
+        dst[r] = from_f32<T>(v * inv);
     }
 }
 
@@ -219,46 +359,92 @@ void latent_prep(const float* proj, int ld, int off_q, int q_rank, const float* 
 }
 
 namespace {
-template <typename T, int NC>
-void launch_latent(const float* q, int ldq, const float* gate, int ldg, const void* w_uk, const void* w_uv,
-                   const float* sink, const void* cache, const int32_t* block_table, int table_width,
-                   const int32_t* token_req, const int32_t* positions, const float* inv_freq, int rot_dims, void* out,
-                   int Tn, int H, int dn, int dr, int dv, int rank, int page_size, int total_pages, int window,
-                   float scale, cudaStream_t stream) {
-    const size_t smem = ((size_t)dn + dr + rank + (size_t)LAT_WARPS * rank + 2 * LAT_WARPS) * sizeof(float);
-    DLM_CHECK(smem <= 200 * 1024, "latent_attention: sizes too large for shared memory");
-    auto kern = latent_attention_kernel<T, NC>;
-    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    kern<<<dim3(Tn, H), 32 * LAT_WARPS, smem, stream>>>(
-        q, ldq, gate, ldg, static_cast<const T*>(w_uk), static_cast<const T*>(w_uv), sink, static_cast<const T*>(cache),
-        block_table, table_width, token_req, positions, inv_freq, rot_dims, static_cast<T*>(out), H, dn, dr, dv, rank,
-        page_size, total_pages, window, scale, error_flag_ptr());
+int heads_per_block(int H) {
+    const int groups = (H + LA_HG - 1) / LA_HG;
+    return (H + groups - 1) / groups;
+}
+
+template <typename T, int NCOL>
+void launch_latent(const float* q_lat, const float* q_rot, const float* sink, const void* cache,
+                   const int32_t* block_table, int table_width, const int32_t* token_req, const int32_t* positions,
+                   void* lat, float* partial, int n_splits, int Tn, int H, int dr, int rank, int page_size,
+                   int total_pages, int window, float scale, cudaStream_t stream) {
+    const int hg = heads_per_block(H);
+    const int wpad = (rank + dr + 7) & ~7;
+    const size_t smem = ((size_t)LA_HG * (rank + dr) + LA_HG * LA_KC + 3 * LA_HG) * sizeof(float) +
+                        (size_t)LA_KC * wpad * sizeof(T);
+    DLM_CHECK(smem <= 220 * 1024, "latent_attention: sizes too large for shared memory");
+    auto kern = latent_attention_kernel<T, NCOL>;
+    static size_t allowed = 48 * 1024;
+    if (smem > allowed) {
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        allowed = smem;
+    }
+    kern<<<dim3(Tn, (H + hg - 1) / hg, n_splits), LA_THREADS, smem, stream>>>(
+        q_lat, q_rot, sink, static_cast<const T*>(cache), block_table, table_width, token_req, positions,
+        static_cast<T*>(lat), partial, Tn, H, dr, rank, page_size, total_pages, window, scale, hg, n_splits,
+        error_flag_ptr());
     check_launch("latent_attention");
+    if (n_splits > 1) {
+        latent_merge_kernel<T><<<dim3(Tn, H), 128, 0, stream>>>(partial, n_splits, sink, static_cast<T*>(lat), Tn, H, rank);
+        check_launch("latent_merge");
+    }
 }
 }  // namespace
 
-void latent_attention(const float* q, int ldq, const float* gate, int ldg, const void* w_uk, const void* w_uv,
-                      const float* sink, const void* cache, const int32_t* block_table, int table_width,
-                      const int32_t* token_req, const int32_t* positions, const float* inv_freq, int rot_dims, void* out,
-                      int T, int H, int dn, int dr, int dv, int rank, int page_size, int total_pages, int window,
-                      float scale, int dtype, cudaStream_t stream) {
+int latent_attention_splits(int T, int H, int max_keys, int dtype) {
+    if (dtype == F32 || T <= 0) return 1;       // 32-bit: one order of summation whatever the step holds
+    const int blocks = T * ((H + heads_per_block(H) - 1) / heads_per_block(H));
+    int want = (2 * sm_count() + blocks - 1) / blocks;
+    const int chunks = (max_keys < 1 ? 1 : max_keys) / LA_KC + 1;
+    if (want > chunks) want = chunks;
+    if (want > 32) want = 32;
+    return want < 1 ? 1 : want;
+}
+
+void latent_q_split(const float* q, int ldq, const int32_t* positions, const float* inv_freq, int rot_dims, void* qn,
+                    float* qr, int T, int H, int dn, int dr, int dtype, cudaStream_t stream) {
+    if (T <= 0) return;
+    DLM_CHECK(rot_dims % 2 == 0 && rot_dims >= 0 && rot_dims <= dr, "latent_q_split: rotated dims must be even and <= dr");
+    if (dtype == F32)
+        latent_q_split_kernel<float><<<T, 256, 0, stream>>>(q, ldq, positions, inv_freq, rot_dims, static_cast<float*>(qn),
+                                                           qr, T, H, dn, dr);
+    else
+        latent_q_split_kernel<__nv_bfloat16><<<T, 256, 0, stream>>>(q, ldq, positions, inv_freq, rot_dims,
+                                                                   static_cast<__nv_bfloat16*>(qn), qr, T, H, dn, dr);
+    check_launch("latent_q_split");
+}
+
+void latent_gate_out(const float* val, const float* gate, int ldg, void* out, int T, int H, int dv, int dtype,
+                     cudaStream_t stream) {
+    if (T <= 0) return;
+    if (dtype == F32)
+        latent_gate_out_kernel<float><<<T, 256, 0, stream>>>(val, gate, ldg, static_cast<float*>(out), T, H, dv);
+    else
+        latent_gate_out_kernel<__nv_bfloat16><<<T, 256, 0, stream>>>(val, gate, ldg, static_cast<__nv_bfloat16*>(out), T,
+                                                                    H, dv);
+    check_launch("latent_gate_out");
+}
+
+void latent_attention(const float* q_lat, const float* q_rot, const float* sink, const void* cache,
+                      const int32_t* block_table, int table_width, const int32_t* token_req, const int32_t* positions,
+                      void* lat, float* partial, int n_splits, int T, int H, int dr, int rank, int page_size,
+                      int total_pages, int window, float scale, int dtype, cudaStream_t stream) {
     if (T <= 0) return;
     DLM_CHECK(rank >= 1 && rank <= 1024, "latent_attention: latent size 1..1024");
-    DLM_CHECK(rot_dims % 2 == 0 && rot_dims <= dr, "latent_attention: rotated dims must be even and <= dr");
-#define DLM_LAT(TT, NC)                                                                                              \
-    launch_latent<TT, NC>(q, ldq, gate, ldg, w_uk, w_uv, sink, cache, block_table, table_width, token_req, positions, \
-                          inv_freq, rot_dims, out, T, H, dn, dr, dv, rank, page_size, total_pages, window, scale, stream)
-    const int nc = (rank + 31) / 32;
+    DLM_CHECK(n_splits >= 1 && (n_splits == 1 || partial != nullptr), "latent_attention: splits need a scratch buffer");
+#define DLM_LAT(TT, NC)                                                                                               \
+    launch_latent<TT, NC>(q_lat, q_rot, sink, cache, block_table, table_width, token_req, positions, lat, partial,    \
+                          n_splits, T, H, dr, rank, page_size, total_pages, window, scale, stream)
+    const int nc = (rank + LA_THREADS - 1) / LA_THREADS;
     if (dtype == F32) {
-        if (nc <= 4) DLM_LAT(float, 4);
-        else if (nc <= 8) DLM_LAT(float, 8);
-        else if (nc <= 16) DLM_LAT(float, 16);
-        else DLM_LAT(float, 32);
+        if (nc <= 1) DLM_LAT(float, 1);
+        else if (nc <= 2) DLM_LAT(float, 2);
+        else DLM_LAT(float, 4);
     } else {
-        if (nc <= 4) DLM_LAT(__nv_bfloat16, 4);
-        else if (nc <= 8) DLM_LAT(__nv_bfloat16, 8);
-        else if (nc <= 16) DLM_LAT(__nv_bfloat16, 16);
-        else DLM_LAT(__nv_bfloat16, 32);
+        if (nc <= 1) DLM_LAT(__nv_bfloat16, 1);
+        else if (nc <= 2) DLM_LAT(__nv_bfloat16, 2);
+        else DLM_LAT(__nv_bfloat16, 4);
     }
 #undef DLM_LAT
 }

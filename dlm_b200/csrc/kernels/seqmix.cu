@@ -74,29 +74,29 @@ __global__ void streams_reduce_kernel(const float* __restrict__ xs, const float*
 }
 
 // xs[t, r, :] <- sum_s mix[s, r] xs[t, s, :] + outw[r] * y[t, :], all streams at once from the old ones.
+// SC: the number of streams at compile time (every loop unrolled, the old values in registers).  blockIdx.y cuts
+// a long row into slices so that a step of few tokens still fills the machine.
 constexpr int MAX_STREAMS = 16;
+template <int SC>
 __global__ void streams_update_kernel(float* xs, const float* __restrict__ mix, const float* __restrict__ outw,
-                                      const float* __restrict__ y, int S, int H) {
-    __shared__ float s_mix[MAX_STREAMS * MAX_STREAMS], s_out[MAX_STREAMS];
-    for (int i = threadIdx.x; i < S * S; i += blockDim.x) s_mix[i] = mix[i];
-    for (int i = threadIdx.x; i < S; i += blockDim.x) s_out[i] = outw[i];
+                                      const float* __restrict__ y, int H) {
+    __shared__ float s_mix[SC * SC], s_out[SC];
+    for (int i = threadIdx.x; i < SC * SC; i += blockDim.x) s_mix[i] = mix[i];
+    for (int i = threadIdx.x; i < SC; i += blockDim.x) s_out[i] = outw[i];
     __syncthreads();
     const int t = blockIdx.x;
-    float* r = xs + (long long)t * S * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        float old[MAX_STREAMS];
+    float* r = xs + (long long)t * SC * H;
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < H; i += gridDim.y * blockDim.x) {
+        float old[SC];
 #pragma unroll
-        for (int s = 0; s < MAX_STREAMS; ++s) old[s] = s < S ? r[(long long)s * H + i] : 0.f;
+        for (int s = 0; s < SC; ++s) old[s] = r[(long long)s * H + i];
         const float yv = y[(long long)t * H + i];
 #pragma unroll
-        for (int d = 0; d < MAX_STREAMS; ++d) {
-            if (d < S) {
-                float v = 0.f;
+        for (int d = 0; d < SC; ++d) {
+            float v = 0.f;
 #pragma unroll
-                for (int s = 0; s < MAX_STREAMS; ++s)
-                    if (s < S) v = fmaf(s_mix[s * S + d], old[s], v);
-                r[(long long)d * H + i] = fmaf(s_out[d], yv, v);
-            }
+            for (int s = 0; s < SC; ++s) v = fmaf(s_mix[s * SC + d], old[s], v);
+            r[(long long)d * H + i] = fmaf(s_out[d], yv, v);
         }
     }
 }
@@ -213,116 +213,237 @@ __global__ void gated_rmsnorm_kernel(const float* __restrict__ y, int ldy, const
     }
 }
 
+// ------------------------------------------------------------ pieces of the two scans
+// Four bytes from global to shared memory without a register in between; a group of such copies is waited for
+// with copies_wait<N>() (all but the N newest groups have landed).
+__device__ __forceinline__ void copy4_async(float* dst_smem, const float* src) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst_smem);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void copies_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void copies_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 // ---------------------------------------------------------------- state-space scan
 // Per head: S <- exp(-exp(A_log) dt) S + dt B x^T (S is N x P), y = S^T C + D x, dt = softplus(dt_raw + dt_bias).
-// A block owns (head, request, a chunk of the P columns) and walks the request's tokens in order; thread p owns
-// column p of S, which lives in shared memory as [N][cols] (thread p touches bank p).  Per token the block loads
-// B, C (N each) and its x values into one of two buffers; one barrier a token.
+// A block owns (head, request, a chunk of the P columns) and walks the request's tokens in order.  Column p of S
+// is shared by `parts` neighbouring lanes (a power of two): lane `part` keeps rows part, part + parts, ... in
+// registers (NPT of them), adds up its share of S^T C and the shares meet in a butterfly of shuffles, so the order
+// of every sum is fixed by (N, parts) alone.  The tokens' inputs come in tiles of `tile` tokens (B, C, the block's
+// x columns, dt), copied asynchronously into one of two buffers while the tile before is worked on; within a tile
+// nothing waits for memory.
+template <int NPT>
 __global__ void ssm_scan_kernel(const float* __restrict__ xbc, int ldx, const float* __restrict__ dt_raw, int lddt,
                                 const float* __restrict__ dt_bias, const float* __restrict__ A_log,
                                 const float* __restrict__ D, float* state, const int32_t* __restrict__ cu_q,
-                                const int32_t* __restrict__ state_slot, float* y, int heads, int P, int N, int groups) {
-    extern __shared__ float sm[];
+                                const int32_t* __restrict__ state_slot, float* y, int heads, int P, int N, int groups,
+                                int parts, int tile) {
+    extern __shared__ float sm[];            // [2][tile][2 N + cols + 2]: B, C, x, dt, decay
     const int h = blockIdx.x, r = blockIdx.y;
-    const int cols = blockDim.x;
-    const int p = blockIdx.z * cols + threadIdx.x;
+    const int cols = blockDim.x / parts;
+    const int part = threadIdx.x % parts;
+    const int col = threadIdx.x / parts;
+    const int p0 = blockIdx.z * cols;
+    const int p = p0 + col;
     const bool live = p < P;
-    float* S = sm;                           // [N][cols]
-    float* bc = sm + (size_t)N * cols;       // [2][2 N]
     const int g = h / (heads / groups);
     const int inner = heads * P;
+    const int rl = 2 * N + cols + 2;
     float* st = state + (((long long)state_slot[r] * heads + h) * N) * P;
-    if (live)
-        for (int n = 0; n < N; ++n) S[n * cols + threadIdx.x] = st[(long long)n * P + p];
+    float s[NPT];
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) {
+        const int n = part + parts * i;
+        s[i] = (live && n < N) ? st[(long long)n * P + p] : 0.f;
+    }
     const float a = -expf(A_log[h]), dcoef = D[h], bias = dt_bias[h];
     const int t0 = cu_q[r], t1 = cu_q[r + 1];
-    for (int t = t0; t < t1; ++t) {
-        float* buf = bc + (size_t)((t - t0) & 1) * 2 * N;
-        const float* row = xbc + (long long)t * ldx;
-        for (int i = threadIdx.x; i < 2 * N; i += cols)
-            buf[i] = i < N ? row[inner + g * N + i] : row[inner + groups * N + g * N + (i - N)];
+    const int n_tiles = (t1 - t0 + tile - 1) / tile;
+    auto fetch = [&](int k) {
+        float* buf = sm + (size_t)(k & 1) * tile * rl;
+        const int first = t0 + k * tile, n = min(tile, t1 - first);
+        for (int idx = threadIdx.x; idx < n * (rl - 1); idx += blockDim.x) {
+            const int tok = idx / (rl - 1), i = idx - tok * (rl - 1);
+            const float* row = xbc + (long long)(first + tok) * ldx;
+            float* dst = buf + (size_t)tok * rl + i;
+            if (i < N) copy4_async(dst, row + inner + g * N + i);
+            else if (i < 2 * N) copy4_async(dst, row + inner + groups * N + g * N + (i - N));
+            else if (i < 2 * N + cols) {
+                if (p0 + (i - 2 * N) < P) copy4_async(dst, row + h * P + p0 + (i - 2 * N));
+            } else copy4_async(dst, dt_raw + (long long)(first + tok) * lddt + h);
+        }
+        copies_commit();
+    };
+    if (n_tiles > 0) fetch(0);
+    for (int k = 0; k < n_tiles; ++k) {
+        if (k + 1 < n_tiles) {
+            fetch(k + 1);
+            copies_wait<1>();
+        } else {
+            copies_wait<0>();
+        }
         __syncthreads();
-        if (live) {
-            const float dt = softplus_f(dt_raw[(long long)t * lddt + h] + bias);
-            const float decay = expf(a * dt);
-            const float xv = row[h * P + p];
+        float* buf = sm + (size_t)(k & 1) * tile * rl;
+        const int first = t0 + k * tile, n = min(tile, t1 - first);
+        if (threadIdx.x < n) {
+            float* row = buf + (size_t)threadIdx.x * rl;
+            const float dt = softplus_f(row[2 * N + cols] + bias);
+            row[2 * N + cols] = dt;
+            row[2 * N + cols + 1] = expf(a * dt);
+        }
+        __syncthreads();
+        for (int tok = 0; tok < n; ++tok) {
+            const float* row = buf + (size_t)tok * rl;
+            const float dt = row[2 * N + cols], decay = row[2 * N + cols + 1];
+            const float xv = live ? row[2 * N + col] : 0.f;
             const float dx = dt * xv;
             float acc = 0.f;
-            for (int n = 0; n < N; ++n) {
-                const float s = fmaf(decay, S[n * cols + threadIdx.x], dx * buf[n]);
-                S[n * cols + threadIdx.x] = s;
-                acc = fmaf(s, buf[N + n], acc);
+#pragma unroll
+            for (int i = 0; i < NPT; ++i) {
+                const int nn = part + parts * i;
+                if (nn < N) {
+                    s[i] = fmaf(decay, s[i], dx * row[nn]);
+                    acc = fmaf(s[i], row[N + nn], acc);
+                }
             }
-            y[(long long)t * inner + h * P + p] = fmaf(dcoef, xv, acc);
+            for (int o = parts >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            if (live && part == 0) y[(long long)(first + tok) * inner + h * P + p] = fmaf(dcoef, xv, acc);
         }
+        __syncthreads();                     // the buffer may be filled again
     }
-    if (live)
-        for (int n = 0; n < N; ++n) st[(long long)n * P + p] = S[n * cols + threadIdx.x];
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) {
+        const int n = part + parts * i;
+        if (live && n < N) st[(long long)n * P + p] = s[i];
+    }
 }
 
 // ----------------------------------------------------------------- delta-rule scan
 // Per head, with key channels i and value channels j (d of each):
-//   w = exp(-exp(-1/2) sigmoid(lw)), a = sigmoid(a_raw + a_bias), u = k / sqrt(sum k^2 + 1e-6)
+//   w = exp(-decay_coef sigmoid(lw)), a = sigmoid(a_raw + a_bias), u = k / sqrt(sum k^2 + unit_eps)
 //   S <- diag(w) S - (a u) (u^T S) + k v^T   (both terms read the old S);   o = S^T r
-// A block owns (head, request, a chunk of value columns); thread j owns column j of S ([d][cols] in shared
-// memory).  Per token the block loads r, k, a, w (d each) into one of two buffers; one barrier a token.
+// A block owns (head, request, a chunk of value columns).  Column j of S is shared by `parts` neighbouring lanes,
+// lane `part` keeps rows part, part + parts, ... in registers; sum k^2, u^T S and S^T r are added per lane and
+// meet in a butterfly of shuffles (a fixed order).  Inputs come in tiles of `tile` tokens (r, k, raw a, raw w, the
+// block's v columns) by asynchronous copies into one of two buffers, as in the state-space scan.
+template <int NPT>
 __global__ void delta_scan_kernel(const float* __restrict__ proj, int ld, int off_r, int off_k, int off_v, int off_a,
                                   const float* __restrict__ lw, int ldlw, const float* __restrict__ a_bias, float* state,
                                   const int32_t* __restrict__ cu_q, const int32_t* __restrict__ state_slot, float* o,
-                                  int heads, int d, float unit_eps, float decay_coef) {
-    extern __shared__ float sm[];
+                                  int heads, int d, float unit_eps, float decay_coef, int parts, int tile) {
+    extern __shared__ float sm[];            // [2][tile][4 d + cols]: r, k, a, w, v
     const int h = blockIdx.x, r = blockIdx.y;
-    const int cols = blockDim.x;
-    const int j = blockIdx.z * cols + threadIdx.x;
+    const int cols = blockDim.x / parts;
+    const int part = threadIdx.x % parts;
+    const int col = threadIdx.x / parts;
+    const int j0 = blockIdx.z * cols;
+    const int j = j0 + col;
     const bool live = j < d;
-    float* S = sm;                           // [d][cols]
-    float* vec = sm + (size_t)d * cols;      // [2][4 d]: r, k, a, w
+    const int rl = 4 * d + cols;
     float* st = state + (((long long)state_slot[r] * heads + h) * d) * d;
-    if (live)
-        for (int i = 0; i < d; ++i) S[i * cols + threadIdx.x] = st[(long long)i * d + j];
+    float s[NPT];
+#pragma unroll
+    for (int ii = 0; ii < NPT; ++ii) {
+        const int i = part + parts * ii;
+        s[ii] = (live && i < d) ? st[(long long)i * d + j] : 0.f;
+    }
     const int t0 = cu_q[r], t1 = cu_q[r + 1];
     const int hd = h * d;
-    for (int t = t0; t < t1; ++t) {
-        float* buf = vec + (size_t)((t - t0) & 1) * 4 * d;
-        const float* row = proj + (long long)t * ld;
-        for (int i = threadIdx.x; i < d; i += cols) {
-            buf[i] = row[off_r + hd + i];
-            buf[d + i] = row[off_k + hd + i];
-            buf[2 * d + i] = sigmoid_f(row[off_a + hd + i] + a_bias[hd + i]);
-            buf[3 * d + i] = expf(-decay_coef * sigmoid_f(lw[(long long)t * ldlw + hd + i]));
+    const int n_tiles = (t1 - t0 + tile - 1) / tile;
+    auto fetch = [&](int k) {
+        float* buf = sm + (size_t)(k & 1) * tile * rl;
+        const int first = t0 + k * tile, n = min(tile, t1 - first);
+        for (int idx = threadIdx.x; idx < n * rl; idx += blockDim.x) {
+            const int tok = idx / rl, i = idx - tok * rl;
+            const float* row = proj + (long long)(first + tok) * ld;
+            float* dst = buf + (size_t)tok * rl + i;
+            if (i < d) copy4_async(dst, row + off_r + hd + i);
+            else if (i < 2 * d) copy4_async(dst, row + off_k + hd + (i - d));
+            else if (i < 3 * d) copy4_async(dst, row + off_a + hd + (i - 2 * d));
+            else if (i < 4 * d) copy4_async(dst, lw + (long long)(first + tok) * ldlw + hd + (i - 3 * d));
+            else if (j0 + (i - 4 * d) < d) copy4_async(dst, row + off_v + hd + j0 + (i - 4 * d));
+        }
+        copies_commit();
+    };
+    if (n_tiles > 0) fetch(0);
+    for (int k = 0; k < n_tiles; ++k) {
+        if (k + 1 < n_tiles) {
+            fetch(k + 1);
+            copies_wait<1>();
+        } else {
+            copies_wait<0>();
         }
         __syncthreads();
-        if (live) {
-            const float* br = buf;
-            const float* bk = buf + d;
-            const float* ba = buf + 2 * d;
-            const float* bw = buf + 3 * d;
-            float ss = 0.f;
-            for (int i = 0; i < d; ++i) ss = fmaf(bk[i], bk[i], ss);
-            const float inv = 1.0f / sqrtf(ss + unit_eps);
-            float us = 0.f;                  // u^T S, this column
-            for (int i = 0; i < d; ++i) us = fmaf(bk[i] * inv, S[i * cols + threadIdx.x], us);
-            const float vj = row[off_v + hd + j];
-            float acc = 0.f;
-            for (int i = 0; i < d; ++i) {
-                const float u = bk[i] * inv;
-                float s = bw[i] * S[i * cols + threadIdx.x];
-                s = fmaf(-(ba[i] * u), us, s);
-                s = fmaf(bk[i], vj, s);
-                S[i * cols + threadIdx.x] = s;
-                acc = fmaf(s, br[i], acc);
-            }
-            o[(long long)t * heads * d + hd + j] = acc;
+        float* buf = sm + (size_t)(k & 1) * tile * rl;
+        const int first = t0 + k * tile, n = min(tile, t1 - first);
+        for (int idx = threadIdx.x; idx < n * d; idx += blockDim.x) {       // raw values -> removal rate and decay
+            const int tok = idx / d, i = idx - tok * d;
+            float* row = buf + (size_t)tok * rl;
+            row[2 * d + i] = sigmoid_f(row[2 * d + i] + a_bias[hd + i]);
+            row[3 * d + i] = expf(-decay_coef * sigmoid_f(row[3 * d + i]));
         }
+        __syncthreads();
+        for (int tok = 0; tok < n; ++tok) {
+            const float* br = buf + (size_t)tok * rl;
+            const float* bk = br + d;
+            const float* ba = br + 2 * d;
+            const float* bw = br + 3 * d;
+            float ss = 0.f, us = 0.f;
+#pragma unroll
+            for (int ii = 0; ii < NPT; ++ii) {
+                const int i = part + parts * ii;
+                if (i < d) {
+                    ss = fmaf(bk[i], bk[i], ss);
+                    us = fmaf(bk[i], s[ii], us);        // k^T S; scaled to u^T S below
+                }
+            }
+            for (int x = parts >> 1; x > 0; x >>= 1) {
+                ss += __shfl_xor_sync(0xffffffffu, ss, x);
+                us += __shfl_xor_sync(0xffffffffu, us, x);
+            }
+            const float inv = 1.0f / sqrtf(ss + unit_eps);
+            us *= inv;
+            const float vj = live ? br[4 * d + col] : 0.f;
+            float acc = 0.f;
+#pragma unroll
+            for (int ii = 0; ii < NPT; ++ii) {
+                const int i = part + parts * ii;
+                if (i < d) {
+                    float v = bw[i] * s[ii];
+                    v = fmaf(-(ba[i] * (bk[i] * inv)), us, v);
+                    v = fmaf(bk[i], vj, v);
+                    s[ii] = v;
+                    acc = fmaf(v, br[i], acc);
+                }
+            }
+            for (int x = parts >> 1; x > 0; x >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, x);
+            if (live && part == 0) o[(long long)(first + tok) * heads * d + hd + j] = acc;
+        }
+        __syncthreads();                     // the buffer may be filled again
     }
-    if (live)
-        for (int i = 0; i < d; ++i) st[(long long)i * d + j] = S[i * cols + threadIdx.x];
+#pragma unroll
+    for (int ii = 0; ii < NPT; ++ii) {
+        const int i = part + parts * ii;
+        if (live && i < d) st[(long long)i * d + j] = s[ii];
+    }
 }
 
-int scan_cols(int width) {
-    int c = 32;
-    while (c < width && c < 128) c *= 2;
-    return c;
+// Tokens a tile of a scan: 16, fewer when a token's inputs are so wide that two buffers of 16 would not fit.
+int scan_tile(int row_floats) {
+    int t = 16;
+    while (t > 1 && 2 * (size_t)t * row_floats * sizeof(float) > 96 * 1024) t /= 2;
+    return t;
+}
+
+// How a column's rows are dealt to lanes: `parts` lanes (a power of two, at most 32) with at most `per` rows each.
+void scan_layout(int rows, int width, int per, int* parts, int* cols, int* chunks) {
+    int pt = 1;
+    while (pt < 32 && (rows + pt - 1) / pt > per) pt *= 2;
+    const int unit = 32 / pt;                               // columns a warp holds
+    int c = ((width + unit - 1) / unit) * unit;
+    if (c > 256 / pt) c = 256 / pt;
+    *parts = pt;
+    *cols = c;
+    *chunks = (width + c - 1) / c;
 }
 
 }  // namespace
@@ -362,7 +483,14 @@ void streams_update(float* xs, const float* mix, const float* outw, const float*
                     cudaStream_t stream) {
     if (T <= 0) return;
     DLM_CHECK(S >= 1 && S <= MAX_STREAMS, "streams_update: at most 16 residual streams");
-    streams_update_kernel<<<T, 256, 0, stream>>>(xs, mix, outw, y, S, H);
+    const int slices = T >= 2 * sm_count() ? 1 : (H + 255) / 256;
+    const dim3 grid(T, slices);
+    switch (S) {
+#define DLM_SU(N) case N: streams_update_kernel<N><<<grid, 256, 0, stream>>>(xs, mix, outw, y, H); break;
+        DLM_SU(1) DLM_SU(2) DLM_SU(3) DLM_SU(4) DLM_SU(5) DLM_SU(6) DLM_SU(7) DLM_SU(8) DLM_SU(9) DLM_SU(10) DLM_SU(11)
+        DLM_SU(12) DLM_SU(13) DLM_SU(14) DLM_SU(15) DLM_SU(16)
+#undef DLM_SU
+    }
     check_launch("streams_update");
 }
 
@@ -424,16 +552,26 @@ void ssm_scan(const float* xbc, int ldx, const float* dt_raw, int lddt, const fl
               int P, int N, int groups, cudaStream_t stream) {
     if (R <= 0) return;
     DLM_CHECK(groups >= 1 && heads % groups == 0, "ssm_scan: heads must be a multiple of groups");
-    const int cols = scan_cols(P);
-    const size_t smem = ((size_t)N * cols + 4 * (size_t)N) * sizeof(float);
-    DLM_CHECK(smem <= 220 * 1024, "ssm_scan: the state of a head does not fit in shared memory");
-    static size_t allowed = 48 * 1024;
-    if (smem > allowed) {
-        cudaFuncSetAttribute(ssm_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        allowed = smem;
-    }
-    ssm_scan_kernel<<<dim3(heads, R, (P + cols - 1) / cols), cols, smem, stream>>>(
-        xbc, ldx, dt_raw, lddt, dt_bias, A_log, D, state, cu_q, state_slot, y, heads, P, N, groups);
+    DLM_CHECK(N >= 1 && N <= 1024, "ssm_scan: state size 1..1024");
+    int parts, cols, chunks;
+    scan_layout(N, P, 8, &parts, &cols, &chunks);     // few rows a lane: many lanes a column, many warps an SM
+    const int per = (N + parts - 1) / parts;
+    const int rl = 2 * N + cols + 2;
+    const int tile = scan_tile(rl);
+    const size_t smem = 2 * (size_t)tile * rl * sizeof(float);
+    DLM_CHECK(smem <= 200 * 1024, "ssm_scan: a token's inputs do not fit in shared memory");
+    const dim3 grid(heads, R, chunks);
+#define DLM_SSM(NPT)                                                                                                  \
+    do {                                                                                                              \
+        if (smem > 48 * 1024)                                                                                         \
+            cudaFuncSetAttribute(ssm_scan_kernel<NPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
+        ssm_scan_kernel<NPT><<<grid, cols * parts, smem, stream>>>(xbc, ldx, dt_raw, lddt, dt_bias, A_log, D, state,  \
+                                                                  cu_q, state_slot, y, heads, P, N, groups, parts, tile); \
+    } while (0)
+    if (per <= 8) DLM_SSM(8);
+    else if (per <= 16) DLM_SSM(16);
+    else DLM_SSM(32);
+#undef DLM_SSM
     check_launch("ssm_scan");
 }
 
@@ -441,17 +579,27 @@ void delta_scan(const float* proj, int ld, int off_r, int off_k, int off_v, int 
                 const float* a_bias, float* state, const int32_t* cu_q, const int32_t* state_slot, float* o, int R,
                 int heads, int d, float unit_eps, float decay_coef, cudaStream_t stream) {
     if (R <= 0) return;
-    const int cols = scan_cols(d);
-    const size_t smem = ((size_t)d * cols + 8 * (size_t)d) * sizeof(float);
-    DLM_CHECK(smem <= 220 * 1024, "delta_scan: the state of a head does not fit in shared memory");
-    static size_t allowed = 48 * 1024;
-    if (smem > allowed) {
-        cudaFuncSetAttribute(delta_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        allowed = smem;
-    }
-    delta_scan_kernel<<<dim3(heads, R, (d + cols - 1) / cols), cols, smem, stream>>>(
-        proj, ld, off_r, off_k, off_v, off_a, lw, ldlw, a_bias, state, cu_q, state_slot, o, heads, d, unit_eps,
-        decay_coef);
+    DLM_CHECK(d >= 1 && d <= 512, "delta_scan: head size 1..512");
+    int parts, cols, chunks;
+    scan_layout(d, d, 4, &parts, &cols, &chunks);
+    const int per = (d + parts - 1) / parts;
+    const int rl = 4 * d + cols;
+    const int tile = scan_tile(rl);
+    const size_t smem = 2 * (size_t)tile * rl * sizeof(float);
+    DLM_CHECK(smem <= 200 * 1024, "delta_scan: a token's inputs do not fit in shared memory");
+    const dim3 grid(heads, R, chunks);
+#define DLM_DELTA(NPT)                                                                                                \
+    do {                                                                                                              \
+        if (smem > 48 * 1024)                                                                                         \
+            cudaFuncSetAttribute(delta_scan_kernel<NPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
+        delta_scan_kernel<NPT><<<grid, cols * parts, smem, stream>>>(proj, ld, off_r, off_k, off_v, off_a, lw, ldlw,  \
+                                                                    a_bias, state, cu_q, state_slot, o, heads, d,     \
+                                                                    unit_eps, decay_coef, parts, tile);               \
+    } while (0)
+    if (per <= 4) DLM_DELTA(4);
+    else if (per <= 8) DLM_DELTA(8);
+    else DLM_DELTA(16);
+#undef DLM_DELTA
     check_launch("delta_scan");
 }
 

@@ -223,21 +223,56 @@ class NativeOps:
                            _p(cq), _p(cache), page_size, total_pages, T, _dt(out_dtype), self._stream())
         return cq
 
-    def latent_attention(self, q, gate, w_uk, w_uv, sink, cache, block_table, batch, inv_freq, rot_dims, H, dn, dr,
-                         dv, rank, window, scale):
-        """Windowed attention over the cached latents with a sink and a gate per head; returns ``[T, H * dv]``
-        in the cache's dtype."""
+    def latent_q_split(self, q, positions, inv_freq, rot_dims, H, dn, dr, out_dtype):
+        """Per head ``[dn plain | dr to be rotated]`` of ``q [T, H * (dn + dr)]`` (32-bit) -> the plain parts head by
+        head ``[H, T, dn]`` in ``out_dtype`` and the rotated parts ``[T, H, dr]`` in 32-bit."""
         T = q.shape[0]
-        total_pages, _, page_size, width = cache.shape
-        assert q.dtype == torch.float32 and q.shape[1] == H * (dn + dr) and width == rank + dr
-        assert w_uk.shape == (H * dn, rank) and w_uv.shape == (H * dv, rank) and w_uk.dtype == cache.dtype
-        out = torch.empty((T, H * dv), dtype=cache.dtype, device=q.device)
+        assert q.dtype == torch.float32 and q.shape[1] == H * (dn + dr) and q.stride(1) == 1
+        qn = torch.empty((H, T, dn), dtype=out_dtype, device=q.device)
+        qr = torch.empty((T, H, dr), dtype=torch.float32, device=q.device)
         self.launches += 1
-        self.k.latent_attention(_p(q), q.stride(0), _p(gate), 0 if gate is None else gate.stride(0), _p(w_uk),
-                                _p(w_uv), _p(sink), _p(cache), _p(block_table), block_table.shape[1],
-                                _p(batch.token_req), _p(batch.positions), _p(inv_freq), int(rot_dims), _p(out), T, H, dn,
-                                dr, dv, rank, page_size, total_pages, int(window), float(scale), _dt(cache.dtype),
-                                self._stream())
+        self.k.latent_q_split(_p(q), q.stride(0), _p(positions), _p(inv_freq), int(rot_dims), _p(qn), _p(qr), T, H, dn,
+                              dr, _dt(out_dtype), self._stream())
+        return qn, qr
+
+    def head_offsets(self, H, T, device):
+        """``[0, T, 2T, ..., H T]``: the groups of a grouped product whose groups are heads (kept: built once)."""
+        key = (H, T, str(device))
+        cache = self.__dict__.setdefault("_head_offsets", {})
+        if key not in cache:
+            if len(cache) > 4096:
+                cache.clear()
+            cache[key] = torch.arange(0, (H + 1) * T, T, dtype=torch.int32, device=device)
+        return cache[key]
+
+    def latent_attention(self, q_lat, q_rot, sink, cache, block_table, batch, H, dr, rank, window, scale):
+        """Windowed attention over the cached latents with a sink per head.  ``q_lat [H, T, rank]`` (32-bit): the
+        queries through W_uk; ``q_rot [T, H, dr]``.  Returns the normalised weighted sums of latent rows,
+        ``[H, T, rank]`` in the cache's dtype."""
+        T = q_rot.shape[0]
+        total_pages, _, page_size, width = cache.shape
+        assert q_lat.dtype == torch.float32 and q_lat.shape == (H, T, rank) and q_rot.shape == (T, H, dr)
+        assert width == rank + dr and q_lat.is_contiguous() and q_rot.is_contiguous()
+        lat = torch.empty((H, T, rank), dtype=cache.dtype, device=q_lat.device)
+        # few tokens (a decode step): every token's keys are cut over several blocks and merged by a second kernel
+        longest = getattr(batch, "max_kv_len", 0) or page_size * block_table.shape[1]
+        max_keys = min(int(window), longest) if window else longest
+        splits = self.k.latent_attention_splits(T, H, int(max_keys), _dt(cache.dtype)) if self.fast else 1
+        partial = torch.empty((T * H * splits * (rank + 2),), dtype=torch.float32, device=q_lat.device) if splits > 1 else None
+        self.launches += 2 if splits > 1 else 1
+        self.k.latent_attention(_p(q_lat), _p(q_rot), _p(sink), _p(cache), _p(block_table), block_table.shape[1],
+                                _p(batch.token_req), _p(batch.positions), _p(lat), _p(partial), splits, T, H, dr, rank,
+                                page_size, total_pages, int(window), float(scale), _dt(cache.dtype), self._stream())
+        return lat
+
+    def latent_gate_out(self, val, gate, H, dv, out_dtype):
+        """``out[t, h * dv + d] = val[h, t, d] * sigmoid(gate[t, h])`` (``gate`` None: 1) in ``out_dtype``."""
+        T = val.shape[0] // H
+        assert val.dtype == torch.float32 and val.shape == (H * T, dv) and val.is_contiguous()
+        out = torch.empty((T, H * dv), dtype=out_dtype, device=val.device)
+        self.launches += 1
+        self.k.latent_gate_out(_p(val), _p(gate), 0 if gate is None else gate.stride(0), _p(out), T, H, dv,
+                               _dt(out_dtype), self._stream())
         return out
 
     def rmsnorm(self, x, w, eps, out_dtype, rows=None):

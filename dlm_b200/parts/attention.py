@@ -92,7 +92,8 @@ class LatentAttention(Mixer):
 
     Only ``[c | rotated k_rot]`` is cached (one paged tensor, ``kv_rank + rot_dim`` wide).  The kernels work on
     the latent: ``q' = W_uk,n^T q_plain`` meets c directly and the weighted sum of latents goes through
-    ``W_uv,n`` at the end, so neither keys nor values of a head are ever built."""
+    ``W_uv,n`` at the end, so neither keys nor values of a head are ever built.  Both per-head products are one
+    grouped matrix product each, with the heads as groups (``latent_attend``)."""
 
     def __init__(self, hidden_size: int, heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int, q_rank: int,
                  eps: float, rope_base: float, rope_dims: int | None = None, window: int | None = None,
@@ -127,7 +128,10 @@ class LatentAttention(Mixer):
         if self.has_gate:
             rows.append(rt.matrix(tensors["g"]))
         self.w_in = torch.cat(rows, dim=0).contiguous()
-        self.w_uq, self.w_uk, self.w_uv = (rt.matrix(tensors[n]) for n in ("uq", "uk", "uv"))
+        self.w_uq = rt.matrix(tensors["uq"])
+        # per head: W_uk transposed ([rank, dim]: the product's rows are latent entries) and W_uv as it is
+        self.w_ukT = rt.matrix(tensors["uk"]).reshape(self.H, self.dn, self.rank).transpose(1, 2).contiguous()
+        self.w_uv = rt.matrix(tensors["uv"]).reshape(self.H, self.dv, self.rank).contiguous()
         self.w_o = rt.matrix(tensors["o"])
         self.qn, self.kvn = rt.vector(tensors["dq.norm"]), rt.vector(tensors["dkv.norm"])
         self.sink = rt.vector(tensors["sink"]) if self.has_sink else None
@@ -147,10 +151,26 @@ class LatentAttention(Mixer):
                              rt.dtype)
         q = ops.linear(cq, self.w_uq, None, torch.float32)
         gate = proj[:, self.q_rank + self.rank + self.dr:] if self.has_gate else None
-        o = ops.latent_attention(q, gate, self.w_uk, self.w_uv, self.sink, cache, view.group.block_table, b, self._freq,
-                                 self.rope_dims, self.H, self.dn, self.dr, self.dv, self.rank, self.window or 0,
-                                 self.scale)
+        o = latent_attend(ops, q, gate, self.w_ukT, self.w_uv, self.sink, cache, view.group.block_table, b, self._freq,
+                          self.rope_dims, self.window or 0, self.scale)
         ops.linear_add(o, self.w_o, resid)
+
+
+def latent_attend(ops, q, gate, w_ukT, w_uv, sink, cache, block_table, batch, inv_freq, rot_dims, window, scale):
+    """From projected queries to gated head outputs ``[T, H * vdim]`` over a cache of latents ``[c | k_rot]``.
+    ``q [T, H * (dim + rot_dim)]`` 32-bit, ``gate [T, H]`` raw or None, ``w_ukT [H, rank, dim]``,
+    ``w_uv [H, vdim, rank]``: split and rotate the queries; take the plain parts through W_uk (a grouped product,
+    heads as groups); attend over the latent rows; take the weighted latents through W_uv (grouped again); gate."""
+    H, rank, dn = w_ukT.shape
+    dv = w_uv.shape[1]
+    T = q.shape[0]
+    dr = q.shape[1] // H - dn
+    qn, q_rot = ops.latent_q_split(q, batch.positions, inv_freq, rot_dims, H, dn, dr, cache.dtype)
+    offsets = ops.head_offsets(H, T, q.device)
+    q_lat = ops.grouped_linear(qn.reshape(H * T, dn), w_ukT, offsets).reshape(H, T, rank)
+    lat = ops.latent_attention(q_lat, q_rot, sink, cache, block_table, batch, H, dr, rank, window, scale)
+    val = ops.grouped_linear(lat.reshape(H * T, rank), w_uv, offsets)
+    return ops.latent_gate_out(val, gate, H, dv, cache.dtype)
 
 
 register_part("mixer", "gqa_attention", GroupedQueryAttention)

@@ -159,30 +159,39 @@ class PlainOps:
             cache[sl[ok] // ps, 0, sl[ok] % ps, :] = torch.cat([c, kr], dim=-1)[ok].to(cache.dtype)
         return cq
 
-    def latent_attention(self, q, gate, w_uk, w_uv, sink, cache, block_table, batch, inv_freq, rot_dims, H, dn, dr,
-                         dv, rank, window, scale):
+    def latent_q_split(self, q, positions, inv_freq, rot_dims, H, dn, dr, out_dtype):
         T = q.shape[0]
-        ps = cache.shape[2]
         q = q.reshape(T, H, dn + dr)
-        q_rot = self._rotate(q[..., dn:], batch.positions, inv_freq, rot_dims)
-        q_lat = torch.einsum("thd,hdr->thr", q[..., :dn], _f(w_uk).reshape(H, dn, rank))
-        out = torch.zeros((T, H, dv), dtype=torch.float32, device=q.device)
+        qn = q[..., :dn].transpose(0, 1).contiguous().to(out_dtype)
+        return qn, self._rotate(q[..., dn:], positions, inv_freq, rot_dims).contiguous()
+
+    def head_offsets(self, H, T, device):
+        return torch.arange(0, (H + 1) * T, T, dtype=torch.int32, device=device)
+
+    def latent_attention(self, q_lat, q_rot, sink, cache, block_table, batch, H, dr, rank, window, scale):
+        T = q_rot.shape[0]
+        ps = cache.shape[2]
+        out = torch.zeros((H, T, rank), dtype=torch.float32, device=q_lat.device)
         req, pos = batch.token_req.tolist(), batch.positions.tolist()
-        wv = _f(w_uv).reshape(H, dv, rank)
         for t in range(T):
             lo = max(0, pos[t] - window + 1) if window > 0 else 0
-            js = torch.arange(lo, pos[t] + 1, device=q.device)
+            js = torch.arange(lo, pos[t] + 1, device=q_lat.device)
             pages = block_table[req[t], (js // ps).long()].long()
             assert int(pages.min()) >= 0, "a visible key has no page"
             rows = _f(cache[pages, 0, js % ps, :])                     # [n, rank + dr]
-            s = (q_lat[t] @ rows[:, :rank].T + q_rot[t] @ rows[:, rank:].T) * scale      # [H, n]
+            s = (q_lat[:, t] @ rows[:, :rank].T + q_rot[t] @ rows[:, rank:].T) * scale      # [H, n]
             if sink is not None:
                 s = torch.cat([s, sink[:, None]], dim=1)
             p = torch.softmax(s, dim=-1)[:, :js.numel()]
-            out[t] = torch.einsum("hr,hdr->hd", p @ rows[:, :rank], wv)
+            out[:, t] = p @ rows[:, :rank]
+        return out.to(cache.dtype)
+
+    def latent_gate_out(self, val, gate, H, dv, out_dtype):
+        T = val.shape[0] // H
+        out = val.reshape(H, T, dv).transpose(0, 1)
         if gate is not None:
             out = out * torch.sigmoid(gate)[:, :, None]
-        return out.reshape(T, H * dv).to(cache.dtype)
+        return out.reshape(T, H * dv).to(out_dtype)
 
     def rmsnorm(self, x, w, eps, out_dtype, rows=None):
         if rows is not None:

@@ -256,14 +256,19 @@ def _latent_case(ops, dtype, H, dn, dr, dv, rank, window, page, lens, starts, se
 
 
 def _run_latent(ops, c, scale=0.3, **over):
+    """The whole way from projected queries to gated head outputs, on the kernels and on their plain statements."""
+    from dlm_b200.parts.attention import latent_attend
     p = dict(c, **over)
     H, dn, dr, dv, rank, window = p["args"]
-    got = ops.latent_attention(p["q"], p["gate"], p["w_uk"], p["w_uv"], p["sink"], p["cache"], p["table"], p["b"],
-                               p["inv_freq"], p["rot_dims"], H, dn, dr, dv, rank, window, scale)
-    want = p["ref"].latent_attention(p["q"].cpu(), None if p["gate"] is None else p["gate"].cpu(), p["w_uk"].cpu(),
-                                     p["w_uv"].cpu(), None if p["sink"] is None else p["sink"].cpu(), p["cache"].cpu(),
-                                     p["table"].cpu(), to_cpu(p["b"]), p["inv_freq"].cpu(), p["rot_dims"], H, dn, dr, dv,
-                                     rank, window, scale)
+    w_ukT = p["w_uk"].reshape(H, dn, rank).transpose(1, 2).contiguous()
+    w_uv = p["w_uv"].reshape(H, dv, rank).contiguous()
+
+    def cpu(v):
+        return v.cpu() if torch.is_tensor(v) else v
+    got = latent_attend(ops, p["q"], p["gate"], w_ukT, w_uv, p["sink"], p["cache"], p["table"], p["b"], p["inv_freq"],
+                        p["rot_dims"], window, scale)
+    want = latent_attend(p["ref"], cpu(p["q"]), cpu(p["gate"]), w_ukT.cpu(), w_uv.cpu(), cpu(p["sink"]), p["cache"].cpu(),
+                         p["table"].cpu(), to_cpu(p["b"]), p["inv_freq"].cpu(), p["rot_dims"], window, scale)
     return got.float().cpu(), want.float()
 
 
