@@ -231,7 +231,9 @@ template <int N> __device__ __forceinline__ void copies_wait() { asm volatile("c
 // of every sum is fixed by (N, parts) alone.  The tokens' inputs come in tiles of `tile` tokens (B, C, the block's
 // x columns, dt), copied asynchronously into one of two buffers while the tile before is worked on; within a tile
 // nothing waits for memory.
-template <int NPT>
+// VEC (N a multiple of 4): a lane's rows come in fours, 4 part + e + 4 parts q, so that B and C are read with
+// 16-byte shared loads that neighbouring lanes take from neighbouring addresses.
+template <int NPT, bool VEC>
 __global__ void ssm_scan_kernel(const float* __restrict__ xbc, int ldx, const float* __restrict__ dt_raw, int lddt,
                                 const float* __restrict__ dt_bias, const float* __restrict__ A_log,
                                 const float* __restrict__ D, float* state, const int32_t* __restrict__ cu_q,
@@ -247,12 +249,13 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, int ldx, const fl
     const bool live = p < P;
     const int g = h / (heads / groups);
     const int inner = heads * P;
-    const int rl = 2 * N + cols + 2;
+    const int rl = (2 * N + cols + 2 + 3) & ~3;
     float* st = state + (((long long)state_slot[r] * heads + h) * N) * P;
+    auto row_of = [&](int i) { return VEC ? 4 * part + (i & 3) + 4 * parts * (i >> 2) : part + parts * i; };
     float s[NPT];
 #pragma unroll
     for (int i = 0; i < NPT; ++i) {
-        const int n = part + parts * i;
+        const int n = row_of(i);
         s[i] = (live && n < N) ? st[(long long)n * P + p] : 0.f;
     }
     const float a = -expf(A_log[h]), dcoef = D[h], bias = dt_bias[h];
@@ -261,8 +264,9 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, int ldx, const fl
     auto fetch = [&](int k) {
         float* buf = sm + (size_t)(k & 1) * tile * rl;
         const int first = t0 + k * tile, n = min(tile, t1 - first);
-        for (int idx = threadIdx.x; idx < n * (rl - 1); idx += blockDim.x) {
-            const int tok = idx / (rl - 1), i = idx - tok * (rl - 1);
+        const int items = 2 * N + cols + 1;
+        for (int idx = threadIdx.x; idx < n * items; idx += blockDim.x) {
+            const int tok = idx / items, i = idx - tok * items;
             const float* row = xbc + (long long)(first + tok) * ldx;
             float* dst = buf + (size_t)tok * rl + i;
             if (i < N) copy4_async(dst, row + inner + g * N + i);
@@ -297,12 +301,31 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, int ldx, const fl
             const float xv = live ? row[2 * N + col] : 0.f;
             const float dx = dt * xv;
             float acc = 0.f;
+            if (VEC) {
 #pragma unroll
-            for (int i = 0; i < NPT; ++i) {
-                const int nn = part + parts * i;
-                if (nn < N) {
-                    s[i] = fmaf(decay, s[i], dx * row[nn]);
-                    acc = fmaf(s[i], row[N + nn], acc);
+                for (int q = 0; q < NPT / 4; ++q) {
+                    const int nn = 4 * part + 4 * parts * q;
+                    if (nn < N) {
+                        const float4 bv = *reinterpret_cast<const float4*>(row + nn);
+                        const float4 cv = *reinterpret_cast<const float4*>(row + N + nn);
+                        s[4 * q + 0] = fmaf(decay, s[4 * q + 0], dx * bv.x);
+                        s[4 * q + 1] = fmaf(decay, s[4 * q + 1], dx * bv.y);
+                        s[4 * q + 2] = fmaf(decay, s[4 * q + 2], dx * bv.z);
+                        s[4 * q + 3] = fmaf(decay, s[4 * q + 3], dx * bv.w);
+                        acc = fmaf(s[4 * q + 0], cv.x, acc);
+                        acc = fmaf(s[4 * q + 1], cv.y, acc);
+                        acc = fmaf(s[4 * q + 2], cv.z, acc);
+                        acc = fmaf(s[4 * q + 3], cv.w, acc);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < NPT; ++i) {
+                    const int nn = part + parts * i;
+                    if (nn < N) {
+                        s[i] = fmaf(decay, s[i], dx * row[nn]);
+                        acc = fmaf(s[i], row[N + nn], acc);
+                    }
                 }
             }
             for (int o = parts >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
@@ -312,7 +335,7 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, int ldx, const fl
     }
 #pragma unroll
     for (int i = 0; i < NPT; ++i) {
-        const int n = part + parts * i;
+        const int n = row_of(i);
         if (live && n < N) st[(long long)n * P + p] = s[i];
     }
 }
@@ -325,7 +348,7 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, int ldx, const fl
 // lane `part` keeps rows part, part + parts, ... in registers; sum k^2, u^T S and S^T r are added per lane and
 // meet in a butterfly of shuffles (a fixed order).  Inputs come in tiles of `tile` tokens (r, k, raw a, raw w, the
 // block's v columns) by asynchronous copies into one of two buffers, as in the state-space scan.
-template <int NPT>
+template <int NPT, bool VEC>
 __global__ void delta_scan_kernel(const float* __restrict__ proj, int ld, int off_r, int off_k, int off_v, int off_a,
                                   const float* __restrict__ lw, int ldlw, const float* __restrict__ a_bias, float* state,
                                   const int32_t* __restrict__ cu_q, const int32_t* __restrict__ state_slot, float* o,
@@ -338,12 +361,13 @@ __global__ void delta_scan_kernel(const float* __restrict__ proj, int ld, int of
     const int j0 = blockIdx.z * cols;
     const int j = j0 + col;
     const bool live = j < d;
-    const int rl = 4 * d + cols;
+    const int rl = (4 * d + cols + 3) & ~3;
     float* st = state + (((long long)state_slot[r] * heads + h) * d) * d;
+    auto row_of = [&](int ii) { return VEC ? 4 * part + (ii & 3) + 4 * parts * (ii >> 2) : part + parts * ii; };
     float s[NPT];
 #pragma unroll
     for (int ii = 0; ii < NPT; ++ii) {
-        const int i = part + parts * ii;
+        const int i = row_of(ii);
         s[ii] = (live && i < d) ? st[(long long)i * d + j] : 0.f;
     }
     const int t0 = cu_q[r], t1 = cu_q[r + 1];
@@ -352,8 +376,9 @@ __global__ void delta_scan_kernel(const float* __restrict__ proj, int ld, int of
     auto fetch = [&](int k) {
         float* buf = sm + (size_t)(k & 1) * tile * rl;
         const int first = t0 + k * tile, n = min(tile, t1 - first);
-        for (int idx = threadIdx.x; idx < n * rl; idx += blockDim.x) {
-            const int tok = idx / rl, i = idx - tok * rl;
+        const int items = 4 * d + cols;
+        for (int idx = threadIdx.x; idx < n * items; idx += blockDim.x) {
+            const int tok = idx / items, i = idx - tok * items;
             const float* row = proj + (long long)(first + tok) * ld;
             float* dst = buf + (size_t)tok * rl + i;
             if (i < d) copy4_async(dst, row + off_r + hd + i);
@@ -388,13 +413,33 @@ __global__ void delta_scan_kernel(const float* __restrict__ proj, int ld, int of
             const float* ba = br + 2 * d;
             const float* bw = br + 3 * d;
             float ss = 0.f, us = 0.f;
+            float kk[NPT], ww[NPT], aa[NPT], rr[NPT];   // this lane's rows of k, w, a, r
 #pragma unroll
-            for (int ii = 0; ii < NPT; ++ii) {
-                const int i = part + parts * ii;
-                if (i < d) {
-                    ss = fmaf(bk[i], bk[i], ss);
-                    us = fmaf(bk[i], s[ii], us);        // k^T S; scaled to u^T S below
+            for (int ii = 0; ii < NPT; ++ii) kk[ii] = ww[ii] = aa[ii] = rr[ii] = 0.f;
+            if (VEC) {
+#pragma unroll
+                for (int q = 0; q < NPT / 4; ++q) {
+                    const int i = 4 * part + 4 * parts * q;
+                    if (i < d) {
+                        const float4 k4 = *reinterpret_cast<const float4*>(bk + i), w4 = *reinterpret_cast<const float4*>(bw + i);
+                        const float4 a4 = *reinterpret_cast<const float4*>(ba + i), r4 = *reinterpret_cast<const float4*>(br + i);
+                        kk[4 * q] = k4.x; kk[4 * q + 1] = k4.y; kk[4 * q + 2] = k4.z; kk[4 * q + 3] = k4.w;
+                        ww[4 * q] = w4.x; ww[4 * q + 1] = w4.y; ww[4 * q + 2] = w4.z; ww[4 * q + 3] = w4.w;
+                        aa[4 * q] = a4.x; aa[4 * q + 1] = a4.y; aa[4 * q + 2] = a4.z; aa[4 * q + 3] = a4.w;
+                        rr[4 * q] = r4.x; rr[4 * q + 1] = r4.y; rr[4 * q + 2] = r4.z; rr[4 * q + 3] = r4.w;
+                    }
                 }
+            } else {
+#pragma unroll
+                for (int ii = 0; ii < NPT; ++ii) {
+                    const int i = part + parts * ii;
+                    if (i < d) { kk[ii] = bk[i]; ww[ii] = bw[i]; aa[ii] = ba[i]; rr[ii] = br[i]; }
+                }
+            }
+#pragma unroll
+            for (int ii = 0; ii < NPT; ++ii) {          // rows beyond d hold zeros and add nothing
+                ss = fmaf(kk[ii], kk[ii], ss);
+                us = fmaf(kk[ii], s[ii], us);           // k^T S; scaled to u^T S below
             }
             for (int x = parts >> 1; x > 0; x >>= 1) {
                 ss += __shfl_xor_sync(0xffffffffu, ss, x);
@@ -406,14 +451,11 @@ __global__ void delta_scan_kernel(const float* __restrict__ proj, int ld, int of
             float acc = 0.f;
 #pragma unroll
             for (int ii = 0; ii < NPT; ++ii) {
-                const int i = part + parts * ii;
-                if (i < d) {
-                    float v = bw[i] * s[ii];
-                    v = fmaf(-(ba[i] * (bk[i] * inv)), us, v);
-                    v = fmaf(bk[i], vj, v);
-                    s[ii] = v;
-                    acc = fmaf(v, br[i], acc);
-                }
+                float v = ww[ii] * s[ii];
+                v = fmaf(-(aa[ii] * (kk[ii] * inv)), us, v);
+                v = fmaf(kk[ii], vj, v);
+                s[ii] = v;
+                acc = fmaf(v, rr[ii], acc);
             }
             for (int x = parts >> 1; x > 0; x >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, x);
             if (live && part == 0) o[(long long)(first + tok) * heads * d + hd + j] = acc;
@@ -422,7 +464,7 @@ __global__ void delta_scan_kernel(const float* __restrict__ proj, int ld, int of
     }
 #pragma unroll
     for (int ii = 0; ii < NPT; ++ii) {
-        const int i = part + parts * ii;
+        const int i = row_of(ii);
         if (live && i < d) st[(long long)i * d + j] = s[ii];
     }
 }
@@ -435,9 +477,14 @@ int scan_tile(int row_floats) {
 }
 
 // How a column's rows are dealt to lanes: `parts` lanes (a power of two, at most 32) with at most `per` rows each.
-void scan_layout(int rows, int width, int per, int* parts, int* cols, int* chunks) {
+void scan_layout(int rows, int width, int per, int* parts, int* cols, int* chunks, bool vec = false) {
     int pt = 1;
-    while (pt < 32 && (rows + pt - 1) / pt > per) pt *= 2;
+    if (vec) {                                              // rows are dealt in fours
+        const int quads = rows / 4, per_q = per / 4;
+        while (pt < 32 && (quads + pt - 1) / pt > per_q) pt *= 2;
+    } else {
+        while (pt < 32 && (rows + pt - 1) / pt > per) pt *= 2;
+    }
     const int unit = 32 / pt;                               // columns a warp holds
     int c = ((width + unit - 1) / unit) * unit;
     if (c > 256 / pt) c = 256 / pt;
@@ -554,23 +601,32 @@ void ssm_scan(const float* xbc, int ldx, const float* dt_raw, int lddt, const fl
     DLM_CHECK(groups >= 1 && heads % groups == 0, "ssm_scan: heads must be a multiple of groups");
     DLM_CHECK(N >= 1 && N <= 1024, "ssm_scan: state size 1..1024");
     int parts, cols, chunks;
-    scan_layout(N, P, 8, &parts, &cols, &chunks);     // few rows a lane: many lanes a column, many warps an SM
-    const int per = (N + parts - 1) / parts;
-    const int rl = 2 * N + cols + 2;
+    const bool vec = N % 4 == 0;
+    scan_layout(N, P, 8, &parts, &cols, &chunks, vec);   // few rows a lane: many lanes a column, many warps an SM
+    const int per = vec ? 4 * ((N / 4 + parts - 1) / parts) : (N + parts - 1) / parts;
+    const int rl = (2 * N + cols + 2 + 3) & ~3;
     const int tile = scan_tile(rl);
     const size_t smem = 2 * (size_t)tile * rl * sizeof(float);
     DLM_CHECK(smem <= 200 * 1024, "ssm_scan: a token's inputs do not fit in shared memory");
     const dim3 grid(heads, R, chunks);
-#define DLM_SSM(NPT)                                                                                                  \
+#define DLM_SSM(NPT, V)                                                                                               \
     do {                                                                                                              \
         if (smem > 48 * 1024)                                                                                         \
-            cudaFuncSetAttribute(ssm_scan_kernel<NPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
-        ssm_scan_kernel<NPT><<<grid, cols * parts, smem, stream>>>(xbc, ldx, dt_raw, lddt, dt_bias, A_log, D, state,  \
-                                                                  cu_q, state_slot, y, heads, P, N, groups, parts, tile); \
+            cudaFuncSetAttribute(ssm_scan_kernel<NPT, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
+        ssm_scan_kernel<NPT, V><<<grid, cols * parts, smem, stream>>>(xbc, ldx, dt_raw, lddt, dt_bias, A_log, D, state, \
+                                                                     cu_q, state_slot, y, heads, P, N, groups, parts, \
+                                                                     tile);                                           \
     } while (0)
-    if (per <= 8) DLM_SSM(8);
-    else if (per <= 16) DLM_SSM(16);
-    else DLM_SSM(32);
+    if (vec) {
+        if (per <= 4) DLM_SSM(4, true);
+        else if (per <= 8) DLM_SSM(8, true);
+        else if (per <= 16) DLM_SSM(16, true);
+        else DLM_SSM(32, true);
+    } else {
+        if (per <= 8) DLM_SSM(8, false);
+        else if (per <= 16) DLM_SSM(16, false);
+        else DLM_SSM(32, false);
+    }
 #undef DLM_SSM
     check_launch("ssm_scan");
 }
@@ -581,24 +637,31 @@ void delta_scan(const float* proj, int ld, int off_r, int off_k, int off_v, int 
     if (R <= 0) return;
     DLM_CHECK(d >= 1 && d <= 512, "delta_scan: head size 1..512");
     int parts, cols, chunks;
-    scan_layout(d, d, 4, &parts, &cols, &chunks);
-    const int per = (d + parts - 1) / parts;
-    const int rl = 4 * d + cols;
+    const bool vec = d % 4 == 0;
+    scan_layout(d, d, 4, &parts, &cols, &chunks, vec);
+    const int per = vec ? 4 * ((d / 4 + parts - 1) / parts) : (d + parts - 1) / parts;
+    const int rl = (4 * d + cols + 3) & ~3;
     const int tile = scan_tile(rl);
     const size_t smem = 2 * (size_t)tile * rl * sizeof(float);
     DLM_CHECK(smem <= 200 * 1024, "delta_scan: a token's inputs do not fit in shared memory");
     const dim3 grid(heads, R, chunks);
-#define DLM_DELTA(NPT)                                                                                                \
+#define DLM_DELTA(NPT, V)                                                                                             \
     do {                                                                                                              \
         if (smem > 48 * 1024)                                                                                         \
-            cudaFuncSetAttribute(delta_scan_kernel<NPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
-        delta_scan_kernel<NPT><<<grid, cols * parts, smem, stream>>>(proj, ld, off_r, off_k, off_v, off_a, lw, ldlw,  \
-                                                                    a_bias, state, cu_q, state_slot, o, heads, d,     \
-                                                                    unit_eps, decay_coef, parts, tile);               \
+            cudaFuncSetAttribute(delta_scan_kernel<NPT, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
+        delta_scan_kernel<NPT, V><<<grid, cols * parts, smem, stream>>>(proj, ld, off_r, off_k, off_v, off_a, lw, ldlw, \
+                                                                       a_bias, state, cu_q, state_slot, o, heads, d,  \
+                                                                       unit_eps, decay_coef, parts, tile);            \
     } while (0)
-    if (per <= 4) DLM_DELTA(4);
-    else if (per <= 8) DLM_DELTA(8);
-    else DLM_DELTA(16);
+    if (vec) {
+        if (per <= 4) DLM_DELTA(4, true);
+        else if (per <= 8) DLM_DELTA(8, true);
+        else DLM_DELTA(16, true);
+    } else {
+        if (per <= 4) DLM_DELTA(4, false);
+        else if (per <= 8) DLM_DELTA(8, false);
+        else DLM_DELTA(16, false);
+    }
 #undef DLM_DELTA
     check_launch("delta_scan");
 }
