@@ -189,16 +189,17 @@ void latent_q_split(const float* q, int ldq, const int32_t* positions, const flo
 // [pages, 1, page_size, rank + dr] and lat[H, T, rank] (the normalised weighted sums of latent rows) in `dtype`.
 // A query at position p sees keys j with 0 <= p - j < window (window 0: all).  n_splits (from
 // latent_attention_splits) > 1 cuts every token's keys over that many blocks; `partial` then holds
-// T * H * n_splits * (rank + 2) floats of scratch and a second kernel merges.
+// T * H * n_splits * (rank + 2) floats of scratch and a second kernel merges.  fast != 0 allows the tensor-core
+// kernel (bfloat16, rank a multiple of 128 up to 512, dr a multiple of 8).
 void latent_attention(const float* q_lat, const float* q_rot, const float* sink, const void* cache,
                       const int32_t* block_table, int table_width, const int32_t* token_req, const int32_t* positions,
                       void* lat, float* partial, int n_splits, int T, int H, int dr, int rank, int page_size,
-                      int total_pages, int window, float scale, int dtype, cudaStream_t stream);
+                      int total_pages, int window, float scale, int dtype, int fast, cudaStream_t stream);
 // out[t, h * dv + d] = val[h * T + t, d] * sigmoid(gate[t, h]) in `dtype` (val f32 [H, T, dv]; gate f32 raw, or nullptr)
 void latent_gate_out(const float* val, const float* gate, int ldg, void* out, int T, int H, int dv, int dtype,
                      cudaStream_t stream);
 // Splits that fill the machine for a step of T tokens whose longest visible range is max_keys (1 in 32-bit, where
 // the order of every sum is fixed).
-int latent_attention_splits(int T, int H, int max_keys, int dtype);
+int latent_attention_splits(int T, int H, int rank, int dr, int max_keys, int dtype, int fast);
 
 }  // namespace dlmk

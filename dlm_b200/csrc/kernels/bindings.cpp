@@ -158,13 +158,13 @@ PYBIND11_MODULE(_dlm_kernels, m) {
     });
     m.def("latent_attention", [](u64 q_lat, u64 q_rot, u64 sink, u64 cache, u64 block_table, int table_width,
                                  u64 token_req, u64 positions, u64 lat, u64 partial, int n_splits, int T, int H, int dr,
-                                 int rank, int page_size, int total_pages, int window, float scale, int dtype,
+                                 int rank, int page_size, int total_pages, int window, float scale, int dtype, int fast,
                                  u64 stream) {
         dlmk::latent_attention(ptr<const float>(q_lat), ptr<const float>(q_rot), ptr<const float>(sink),
                                ptr<const void>(cache), ptr<const int32_t>(block_table), table_width,
                                ptr<const int32_t>(token_req), ptr<const int32_t>(positions), ptr<void>(lat),
                                ptr<float>(partial), n_splits, T, H, dr, rank, page_size, total_pages, window, scale, dtype,
-                               st(stream));
+                               fast, st(stream));
     });
     m.def("latent_attention_splits", &dlmk::latent_attention_splits);
     m.def("take_error_flag", &dlmk::take_error_flag);

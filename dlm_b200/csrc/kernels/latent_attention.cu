@@ -11,8 +11,11 @@
 // eight of its heads and reads each row once.  In 32-bit a (token, head)'s result is computed in one order whatever else the step holds (keys
 // go in chunks cut at absolute positions, one after the other); in bfloat16 a step of few tokens cuts each token's
 // keys over several blocks and merges them, which changes the result by rounding only.
+#include <cstdlib>
+
 #include "api.h"
 #include "common.cuh"
+#include "mma_sync.cuh"
 
 namespace dlmk {
 namespace {
@@ -312,6 +315,200 @@ latent_attention_kernel(const float* __restrict__ q_lat, const float* __restrict
     }
 }
 
+// The same on tensor cores (bfloat16, latent size a multiple of 128 up to 512): one block a (token, up to 16 heads,
+// split).  The heads are the 16 rows of m16n8k16 products.  Per chunk of 32 keys: scores S[16 x 32] = Q K^T over the
+// whole row [c | k_rot] (zero-padded to a multiple of 64), warp w taking keys 8 (w % 4) .. and half of the k range;
+// the two halves meet in shared memory where warp w takes the softmax step of rows w and w + 8 in 32-bit; the weights
+// go back as two bfloat16 terms (p = hi + lo, so that the 32-bit weights lose nothing in the product); then
+// O[16 x rank] += P C with warp w owning 8 NT latent columns, its accumulators in registers for the whole walk.
+// NT: 8-column tiles a warp owns (rank = 64 NT).  Queries are rounded to bfloat16 (the product's left operand).
+constexpr int LM_ROWS = 16;
+constexpr int LM_PP = LA_KC + 8;           // row pitch of the weights (bfloat16)
+
+template <int NT>
+__global__ void __launch_bounds__(LA_THREADS)
+latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __restrict__ q_rot,
+                            const float* __restrict__ sink, const __nv_bfloat16* __restrict__ cache,
+                            const int32_t* __restrict__ block_table, int table_width,
+                            const int32_t* __restrict__ token_req, const int32_t* __restrict__ positions,
+                            __nv_bfloat16* lat, float* partial, int Tn, int H, int dr, int rank, int page_size,
+                            int total_pages, int window, float scale, int n_splits, int* err) {
+    typedef __nv_bfloat16 bf16;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int width = rank + dr;
+    const int wk = (width + 63) & ~63;                      // k extent of the score product
+    const int qp = wk + 8;                                  // row pitch: 16 bytes off a multiple of 128
+    bf16* s_q = reinterpret_cast<bf16*>(smem_raw);          // [16][qp]  queries [through W_uk | rotated part]
+    bf16* s_keys = s_q + (size_t)LM_ROWS * qp;              // [32][qp]  the chunk's cache rows
+    bf16* s_pb = s_keys + (size_t)LA_KC * qp;               // [2][16][LM_PP] weights, high and low term
+    float* s_s = reinterpret_cast<float*>(s_pb + 2 * LM_ROWS * LM_PP);   // [2][16][32] scores of the two k halves
+    float* s_m = s_s + 2 * LM_ROWS * LA_KC;                 // [16]
+    float* s_l = s_m + LM_ROWS;
+    float* s_corr = s_l + LM_ROWS;
+    const int t = blockIdx.x;
+    const int h0 = blockIdx.y * LM_ROWS;
+    const int hg = min(LM_ROWS, H - h0);
+    const int ks_id = blockIdx.z;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, tq = lane & 3;
+    const int p = positions[t];
+    for (int idx = threadIdx.x; idx < LM_ROWS * qp; idx += LA_THREADS) {
+        const int row = idx / qp, c = idx - row * qp;
+        float v = 0.f;
+        if (row < hg) {
+            if (c < rank) v = q_lat[((long long)(h0 + row) * Tn + t) * rank + c];
+            else if (c < width) v = q_rot[((long long)t * H + h0 + row) * dr + (c - rank)];
+        }
+        s_q[idx] = __float2bfloat16_rn(v);
+    }
+    for (int idx = threadIdx.x; idx < LA_KC * (qp - width); idx += LA_THREADS) {     // the padding stays zero
+        const int row = idx / (qp - width), c = idx - row * (qp - width);
+        s_keys[(size_t)row * qp + width + c] = __float2bfloat16_rn(0.f);
+    }
+    if (threadIdx.x < LM_ROWS) {
+        s_m[threadIdx.x] = -INFINITY;
+        s_l[threadIdx.x] = 0.f;
+    }
+    float acc[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+
+    const int req = token_req[t];
+    const int32_t* table = block_table + (long long)req * table_width;
+    const int lo = window > 0 ? max(p - window + 1, 0) : 0;
+    const int c_first = lo / LA_KC, c_last = p / LA_KC;
+    const int per = (c_last - c_first + 1 + n_splits - 1) / n_splits;
+    const int c_begin = c_first + ks_id * per, c_end = min(c_begin + per, c_last + 1);
+    const int arow = (lane & 7) + 8 * ((lane >> 3) & 1);    // the row a lane names in a 16-row ldmatrix.x4
+    const int n_base = warp * NT * 8;
+    for (int ch = c_begin; ch < c_end; ++ch) {
+        __syncthreads();                                    // the chunk before is done with s_keys, s_s and s_pb
+        for (int jj = warp; jj < LA_KC; jj += LA_THREADS / 32) {
+            const int j = ch * LA_KC + jj;
+            bf16* dst = s_keys + (size_t)jj * qp;
+            const bf16* row = nullptr;
+            if (j >= lo && j <= p) {
+                const int lp = j / page_size;
+                const int page = lp < table_width ? table[lp] : -1;
+                if (page < 0 || page >= total_pages) {
+                    if (lane == 0) *err = 3;
+                } else {
+                    row = cache + ((long long)page * page_size + (j - lp * page_size)) * width;
+                }
+            }
+            uint4* d4 = reinterpret_cast<uint4*>(dst);
+            if (row == nullptr) {
+                for (int i = lane; i < width / 8; i += 32) d4[i] = make_uint4(0u, 0u, 0u, 0u);
+            } else {
+                const uint4* src = reinterpret_cast<const uint4*>(row);
+                for (int i = lane; i < width / 8; i += 32) d4[i] = src[i];
+            }
+        }
+        __syncthreads();
+        // ---- scores: keys 8 nt .. 8 nt + 7, one half of the k range
+        {
+            const int nt = warp & 3, kh = warp >> 2;
+            const int half = wk / 32;                       // k steps of 16 in a half (even: wk is a multiple of 64)
+            float c[4] = {0.f, 0.f, 0.f, 0.f};
+            const bf16* abase = s_q + (size_t)arow * qp + 8 * (lane >> 4);
+            const bf16* bbase = s_keys + (size_t)(8 * nt + (lane & 7)) * qp + 8 * (lane >> 3);
+            for (int ks = kh * half; ks < (kh + 1) * half; ks += 2) {
+                uint32_t a0[4], a1[4], b[4];
+                ldsm_x4(a0, abase + ks * 16);
+                ldsm_x4(a1, abase + (ks + 1) * 16);
+                ldsm_x4(b, bbase + ks * 16);                // k step ks (two halves), k step ks + 1 (two halves)
+                mma16816(c, a0, b[0], b[1]);
+                mma16816(c, a1, b[2], b[3]);
+            }
+            float* dst = s_s + kh * LM_ROWS * LA_KC;
+            dst[g * LA_KC + 8 * nt + 2 * tq] = c[0];
+            dst[g * LA_KC + 8 * nt + 2 * tq + 1] = c[1];
+            dst[(g + 8) * LA_KC + 8 * nt + 2 * tq] = c[2];
+            dst[(g + 8) * LA_KC + 8 * nt + 2 * tq + 1] = c[3];
+        }
+        __syncthreads();
+        // ---- softmax step of rows warp and warp + 8 (lane = key)
+#pragma unroll
+        for (int rr = 0; rr < 2; ++rr) {
+            const int row = warp + 8 * rr;
+            const int j = ch * LA_KC + lane;
+            float sc = (s_s[row * LA_KC + lane] + s_s[LM_ROWS * LA_KC + row * LA_KC + lane]) * scale;
+            if (j < lo || j > p) sc = -INFINITY;
+            const float m_old = s_m[row];
+            const float m_new = fmaxf(m_old, warp_max(sc));
+            float pw = 0.f, corr = 1.f;
+            if (m_new > -INFINITY) {
+                pw = expf(sc - m_new);
+                corr = expf(m_old - m_new);
+            }
+            const float sum = warp_sum(pw);
+            const bf16 hi = __float2bfloat16_rn(pw);
+            s_pb[row * LM_PP + lane] = hi;
+            s_pb[LM_ROWS * LM_PP + row * LM_PP + lane] = __float2bfloat16_rn(pw - __bfloat162float(hi));
+            if (lane == 0) {
+                s_l[row] = s_l[row] * corr + sum;
+                s_m[row] = m_new;
+                s_corr[row] = corr;
+            }
+        }
+        __syncthreads();
+        // ---- weighted latents: this warp's columns
+        {
+            const float c0 = s_corr[g], c1 = s_corr[g + 8];
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+                acc[n][0] *= c0; acc[n][1] *= c0; acc[n][2] *= c1; acc[n][3] *= c1;
+            }
+#pragma unroll
+            for (int kk = 0; kk < 2; ++kk) {
+                uint32_t ah[4], al[4];
+                const bf16* pa = s_pb + arow * LM_PP + kk * 16 + 8 * (lane >> 4);
+                ldsm_x4(ah, pa);
+                ldsm_x4(al, pa + LM_ROWS * LM_PP);
+                const bf16* kb = s_keys + (size_t)(kk * 16 + arow) * qp + n_base + 8 * (lane >> 4);
+#pragma unroll
+                for (int n = 0; n < NT; n += 2) {
+                    uint32_t b[4];
+                    ldsm_x4_trans(b, kb + n * 8);
+                    mma16816(acc[n], ah, b[0], b[1]);
+                    mma16816(acc[n], al, b[0], b[1]);
+                    mma16816(acc[n + 1], ah, b[2], b[3]);
+                    mma16816(acc[n + 1], al, b[2], b[3]);
+                }
+            }
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+        const int row = g + 8 * rr;
+        if (row >= hg) continue;
+        if (n_splits > 1) {
+            float* dst = partial + (((long long)t * H + h0 + row) * n_splits + ks_id) * (rank + 2);
+            if (warp == 0 && tq == 0) {
+                dst[0] = s_m[row];
+                dst[1] = s_l[row];
+            }
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+                dst[2 + n_base + n * 8 + 2 * tq] = acc[n][2 * rr];
+                dst[2 + n_base + n * 8 + 2 * tq + 1] = acc[n][2 * rr + 1];
+            }
+        } else {
+            const float snk = sink ? sink[h0 + row] : -INFINITY;
+            const float mm = fmaxf(s_m[row], snk);
+            const float f = s_l[row] > 0.f ? expf(s_m[row] - mm) : 0.f;
+            const float den = s_l[row] * f + (sink ? expf(snk - mm) : 0.f);
+            const float w = den > 0.f ? f / den : 0.f;
+            bf16* dst = lat + ((long long)(h0 + row) * Tn + t) * rank;
+#pragma unroll
+            for (int n = 0; n < NT; ++n)
+                *reinterpret_cast<uint32_t*>(dst + n_base + n * 8 + 2 * tq) =
+                    pack_bf16(acc[n][2 * rr] * w, acc[n][2 * rr + 1] * w);
+        }
+    }
+}
+
 // Merges the splits of a (token, head) in order and normalises as above.  One block a (token, head).
 template <typename T>
 __global__ void latent_merge_kernel(const float* __restrict__ partial, int n_splits, const float* __restrict__ sink,
@@ -392,9 +589,22 @@ void launch_latent(const float* q_lat, const float* q_rot, const float* sink, co
 }
 }  // namespace
 
-int latent_attention_splits(int T, int H, int max_keys, int dtype) {
+// The tensor-core kernel takes bfloat16 with a latent of 128, 256, 384 or 512 and a rotated part in multiples of 8
+// (DLM_B200_NO_LATENT_MMA=1 switches it off).
+bool latent_use_mma(int dtype, int rank, int dr, int fast) {
+    static int off = -1;
+    if (off < 0) {
+        const char* e = std::getenv("DLM_B200_NO_LATENT_MMA");
+        off = (e != nullptr && e[0] != '\0' && e[0] != '0') ? 1 : 0;
+    }
+    return fast && !off && dtype == BF16 && rank % 128 == 0 && rank <= 512 && dr % 8 == 0;
+}
+
+int latent_attention_splits(int T, int H, int rank, int dr, int max_keys, int dtype, int fast) {
     if (dtype == F32 || T <= 0) return 1;       // 32-bit: one order of summation whatever the step holds
-    const int blocks = T * ((H + heads_per_block(H) - 1) / heads_per_block(H));
+    const int blocks = latent_use_mma(dtype, rank, dr, fast)
+                           ? T * ((H + LM_ROWS - 1) / LM_ROWS)
+                           : T * ((H + heads_per_block(H) - 1) / heads_per_block(H));
     int want = (2 * sm_count() + blocks - 1) / blocks;
     const int chunks = (max_keys < 1 ? 1 : max_keys) / LA_KC + 1;
     if (want > chunks) want = chunks;
@@ -429,10 +639,39 @@ void latent_gate_out(const float* val, const float* gate, int ldg, void* out, in
 void latent_attention(const float* q_lat, const float* q_rot, const float* sink, const void* cache,
                       const int32_t* block_table, int table_width, const int32_t* token_req, const int32_t* positions,
                       void* lat, float* partial, int n_splits, int T, int H, int dr, int rank, int page_size,
-                      int total_pages, int window, float scale, int dtype, cudaStream_t stream) {
+                      int total_pages, int window, float scale, int dtype, int fast, cudaStream_t stream) {
     if (T <= 0) return;
     DLM_CHECK(rank >= 1 && rank <= 1024, "latent_attention: latent size 1..1024");
     DLM_CHECK(n_splits >= 1 && (n_splits == 1 || partial != nullptr), "latent_attention: splits need a scratch buffer");
+    if (latent_use_mma(dtype, rank, dr, fast)) {
+        const int wk = (rank + dr + 63) & ~63, qp = wk + 8;
+        const size_t smem = ((size_t)(LM_ROWS + LA_KC) * qp + 2 * LM_ROWS * LM_PP) * sizeof(__nv_bfloat16) +
+                            (2 * LM_ROWS * LA_KC + 3 * LM_ROWS) * sizeof(float);
+        const dim3 grid(T, (H + LM_ROWS - 1) / LM_ROWS, n_splits);
+#define DLM_LMMA(NT)                                                                                                  \
+    do {                                                                                                              \
+        auto kern = latent_attention_mma_kernel<NT>;                                                                  \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
+        kern<<<grid, LA_THREADS, smem, stream>>>(q_lat, q_rot, sink, static_cast<const __nv_bfloat16*>(cache),        \
+                                                 block_table, table_width, token_req, positions,                      \
+                                                 static_cast<__nv_bfloat16*>(lat), partial, T, H, dr, rank, page_size, \
+                                                 total_pages, window, scale, n_splits, error_flag_ptr());             \
+    } while (0)
+        switch (rank / 64) {
+            case 2: DLM_LMMA(2); break;
+            case 4: DLM_LMMA(4); break;
+            case 6: DLM_LMMA(6); break;
+            default: DLM_LMMA(8); break;
+        }
+#undef DLM_LMMA
+        check_launch("latent_attention (tensor cores)");
+        if (n_splits > 1) {
+            latent_merge_kernel<__nv_bfloat16><<<dim3(T, H), 128, 0, stream>>>(
+                partial, n_splits, sink, static_cast<__nv_bfloat16*>(lat), T, H, rank);
+            check_launch("latent_merge");
+        }
+        return;
+    }
 #define DLM_LAT(TT, NC)                                                                                               \
     launch_latent<TT, NC>(q_lat, q_rot, sink, cache, block_table, table_width, token_req, positions, lat, partial,    \
                           n_splits, T, H, dr, rank, page_size, total_pages, window, scale, stream)

@@ -257,12 +257,13 @@ class NativeOps:
         # few tokens (a decode step): every token's keys are cut over several blocks and merged by a second kernel
         longest = getattr(batch, "max_kv_len", 0) or page_size * block_table.shape[1]
         max_keys = min(int(window), longest) if window else longest
-        splits = self.k.latent_attention_splits(T, H, int(max_keys), _dt(cache.dtype)) if self.fast else 1
+        splits = self.k.latent_attention_splits(T, H, rank, dr, int(max_keys), _dt(cache.dtype), self.fast)
         partial = torch.empty((T * H * splits * (rank + 2),), dtype=torch.float32, device=q_lat.device) if splits > 1 else None
         self.launches += 2 if splits > 1 else 1
         self.k.latent_attention(_p(q_lat), _p(q_rot), _p(sink), _p(cache), _p(block_table), block_table.shape[1],
                                 _p(batch.token_req), _p(batch.positions), _p(lat), _p(partial), splits, T, H, dr, rank,
-                                page_size, total_pages, int(window), float(scale), _dt(cache.dtype), self._stream())
+                                page_size, total_pages, int(window), float(scale), _dt(cache.dtype), self.fast,
+                                self._stream())
         return lat
 
     def latent_gate_out(self, val, gate, H, dv, out_dtype):

@@ -274,7 +274,10 @@ def _run_latent(ops, c, scale=0.3, **over):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,dn,dr,dv,rank,window,rot_dims", [(3, 24, 16, 40, 48, 7, 8), (2, 40, 8, 24, 72, 16, 8),
-                                                             (4, 64, 32, 64, 160, 33, 32), (1, 16, 24, 16, 300, 0, 24)])
+                                                             (4, 64, 32, 64, 160, 33, 32), (1, 16, 24, 16, 300, 0, 24),
+                                                             # latents the tensor-core kernel takes (in bfloat16)
+                                                             (3, 24, 16, 40, 128, 7, 8), (20, 16, 8, 24, 256, 33, 8),
+                                                             (16, 128, 64, 128, 512, 50, 64), (5, 32, 24, 16, 384, 0, 24)])
 def test_latent_attention_against_its_statement(ops, dtype, H, dn, dr, dv, rank, window, rot_dims):
     """Prompt portions that start in the middle of a page beside single decoded tokens, pages of 16 scattered over
     the pool, windows shorter than, equal to and longer than a page."""
@@ -287,35 +290,36 @@ def test_latent_attention_against_its_statement(ops, dtype, H, dn, dr, dv, rank,
     assert torch.allclose(got2, want2, atol=tol, rtol=tol) and not torch.allclose(got2, got, atol=tol)
 
 
-@pytest.mark.parametrize("window,page", [(16, 16), (17, 16), (5, 16), (64, 64), (40, 64)])
-def test_latent_attention_finds_the_key_at_the_windows_edge(ops, window, page):
+@pytest.mark.parametrize("dtype,rank", [(torch.float32, 32), (torch.bfloat16, 128)])
+@pytest.mark.parametrize("window,page", [(16, 16), (17, 16), (5, 16), (64, 64), (40, 64), (33, 16)])
+def test_latent_attention_finds_the_key_at_the_windows_edge(ops, window, page, dtype, rank):
     """One cached token gets a rotated key part that the query's rotated part loves (no rotation: rot_dims 0).
     A query at distance window - 1 returns that token's value; at distance window it does not see it.  Decoded
     alone and inside a prompt portion, with the key at the last place of a page and at the first of the next."""
-    H, dn, dr, dv, rank = 2, 8, 4, 8, 32
-    for key_pos in (page - 1, page, 2 * page + 3):
-        total = key_pos + window + 2
-        c = _latent_case(ops, torch.float32, H, dn, dr, dv, rank, window, page, lens=[1, 1, 6], starts=[key_pos + window - 1,
+    H, dn, dr, dv = 2, 8, 8, 8
+    tol = 1e-3 if dtype == torch.float32 else 4e-2
+    for key_pos in (page - 1, page, 2 * page + 3, 31, 32):
+        c = _latent_case(ops, dtype, H, dn, dr, dv, rank, window, page, lens=[1, 1, 6], starts=[key_pos + window - 1,
                          key_pos + window, key_pos + window - 3], seed=key_pos, rot_dims=0)
         # the three requests hold the same kind of cache; plant the key in each at key_pos
         cache, table = c["cache"], c["table"]
         for r in range(3):
             pg = int(table[r, key_pos // page])
-            cache[pg, 0, key_pos % page, rank:] = torch.tensor([30.0, 0, 0, 0], device=DEV)
+            cache[pg, 0, key_pos % page, rank:] = torch.tensor([30.0, 0, 0, 0, 0, 0, 0, 0], device=DEV).to(dtype)
         q = torch.zeros_like(c["q"]).reshape(-1, H, dn + dr)
         q[:, :, dn] = 30.0                                   # every query loves that direction
         got, want = _run_latent(ops, c, q=q.reshape(c["q"].shape), gate=None, sink=None, scale=1.0)
-        assert torch.allclose(got, want, atol=1e-4, rtol=1e-4)
+        assert torch.allclose(got, want, atol=tol / 10, rtol=tol / 10)
         wv = c["w_uv"].float().reshape(H, dv, rank)
 
         def value_of(r):
             pg = int(table[r, key_pos // page])
             return torch.einsum("hdr,r->hd", wv, cache[pg, 0, key_pos % page, :rank].float()).reshape(-1).cpu()
-        assert torch.allclose(got[0], value_of(0), atol=1e-3)                      # decoded, distance window - 1: seen
+        assert torch.allclose(got[0], value_of(0), atol=tol)                       # decoded, distance window - 1: seen
         assert not torch.allclose(got[1], value_of(1), atol=1e-1)                  # decoded, distance window: not seen
         # the portion holds positions key_pos + window - 3 .. + 2: the first three see the key, the others do not
         for i in range(6):
-            assert torch.allclose(got[2 + i], value_of(2), atol=1e-3) == (i < 3)
+            assert torch.allclose(got[2 + i], value_of(2), atol=tol if i < 3 else 1e-1) == (i < 3)
 
 
 def test_latent_attention_sink_takes_the_weight(ops):

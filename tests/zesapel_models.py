@@ -9,7 +9,7 @@ X, Y and Z differ in every size and option; none of the sizes is a power of two 
 fast path needs it, and sizes that a config could make equal by accident (dim, rot_dim, vdim; heads
 of the three mixers; state and vdim) are unequal.  Y has one stream, a layer without feed-forward, a
 window equal to a page and a single expert choice; Z has larger heads (128-wide delta heads, 64-wide
-state) for the wide paths.
+state) and a latent of 128 for the wide paths (in bfloat16 its attention runs on the tensor-core kernel).
 """
 from __future__ import annotations
 
@@ -62,7 +62,7 @@ CONFIGS = {
           "embedding": {"scale": 11.3}, "norm": {"eps": 1e-6}, "canon": {"taps": 3},
           "layers": [_with(_delta(2, 128), _moe(6, 2, 64)),
                      _with(_mamba(2, 136, 64, 1, 4, 1), _moe(6, 2, 64)),
-                     _with(_latent(4, 64, 32, 64, 160, 96, 130, 10000.0, scale=0.09), _moe(6, 2, 64))]},
+                     _with(_latent(4, 64, 32, 64, 128, 96, 130, 10000.0, scale=0.09), _moe(6, 2, 64))]},
 }
 
 
