@@ -221,6 +221,10 @@ __device__ __forceinline__ void copy4_async(float* dst_smem, const float* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
 }
 __device__ __forceinline__ void copies_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void copy16_async(float* dst_smem, const float* src) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst_smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+}
 template <int N> __device__ __forceinline__ void copies_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // ---------------------------------------------------------------- state-space scan
@@ -238,8 +242,8 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, int ldx, const fl
                                 const float* __restrict__ dt_bias, const float* __restrict__ A_log,
                                 const float* __restrict__ D, float* state, const int32_t* __restrict__ cu_q,
                                 const int32_t* __restrict__ state_slot, float* y, int heads, int P, int N, int groups,
-                                int parts, int tile) {
-    extern __shared__ float sm[];            // [2][tile][2 N + cols + 2]: B, C, x, dt, decay
+                                int parts, int tile, int wide) {
+    extern __shared__ __align__(16) float sm[];            // [2][tile][2 N + cols + 2]: B, C, x, dt, decay
     const int h = blockIdx.x, r = blockIdx.y;
     const int cols = blockDim.x / parts;
     const int part = threadIdx.x % parts;
@@ -261,19 +265,32 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, int ldx, const fl
     const float a = -expf(A_log[h]), dcoef = D[h], bias = dt_bias[h];
     const int t0 = cu_q[r], t1 = cu_q[r + 1];
     const int n_tiles = (t1 - t0 + tile - 1) / tile;
+    // a warp fetches a token at a time; `wide`: every run starts on a 16-byte boundary and is a multiple of four
     auto fetch = [&](int k) {
         float* buf = sm + (size_t)(k & 1) * tile * rl;
         const int first = t0 + k * tile, n = min(tile, t1 - first);
-        const int items = 2 * N + cols + 1;
-        for (int idx = threadIdx.x; idx < n * items; idx += blockDim.x) {
-            const int tok = idx / items, i = idx - tok * items;
+        const int lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
+        for (int tok = threadIdx.x >> 5; tok < n; tok += nwarp) {
             const float* row = xbc + (long long)(first + tok) * ldx;
-            float* dst = buf + (size_t)tok * rl + i;
-            if (i < N) copy4_async(dst, row + inner + g * N + i);
-            else if (i < 2 * N) copy4_async(dst, row + inner + groups * N + g * N + (i - N));
-            else if (i < 2 * N + cols) {
-                if (p0 + (i - 2 * N) < P) copy4_async(dst, row + h * P + p0 + (i - 2 * N));
-            } else copy4_async(dst, dt_raw + (long long)(first + tok) * lddt + h);
+            const float* srcB = row + inner + g * N;
+            const float* srcC = row + inner + groups * N + g * N;
+            const float* srcX = row + h * P + p0;
+            float* dst = buf + (size_t)tok * rl;
+            const int nx = min(cols, P - p0);
+            if (wide) {
+                for (int i = 4 * lane; i < N; i += 128) {
+                    copy16_async(dst + i, srcB + i);
+                    copy16_async(dst + N + i, srcC + i);
+                }
+                for (int i = 4 * lane; i < nx; i += 128) copy16_async(dst + 2 * N + i, srcX + i);
+            } else {
+                for (int i = lane; i < N; i += 32) {
+                    copy4_async(dst + i, srcB + i);
+                    copy4_async(dst + N + i, srcC + i);
+                }
+                for (int i = lane; i < nx; i += 32) copy4_async(dst + 2 * N + i, srcX + i);
+            }
+            if (lane == 0) copy4_async(dst + 2 * N + cols, dt_raw + (long long)(first + tok) * lddt + h);
         }
         copies_commit();
     };
@@ -352,8 +369,8 @@ template <int NPT, bool VEC>
 __global__ void delta_scan_kernel(const float* __restrict__ proj, int ld, int off_r, int off_k, int off_v, int off_a,
                                   const float* __restrict__ lw, int ldlw, const float* __restrict__ a_bias, float* state,
                                   const int32_t* __restrict__ cu_q, const int32_t* __restrict__ state_slot, float* o,
-                                  int heads, int d, float unit_eps, float decay_coef, int parts, int tile) {
-    extern __shared__ float sm[];            // [2][tile][4 d + cols]: r, k, a, w, v
+                                  int heads, int d, float unit_eps, float decay_coef, int parts, int tile, int wide) {
+    extern __shared__ __align__(16) float sm[];            // [2][tile][4 d + cols]: r, k, a, w, v
     const int h = blockIdx.x, r = blockIdx.y;
     const int cols = blockDim.x / parts;
     const int part = threadIdx.x % parts;
@@ -373,19 +390,33 @@ __global__ void delta_scan_kernel(const float* __restrict__ proj, int ld, int of
     const int t0 = cu_q[r], t1 = cu_q[r + 1];
     const int hd = h * d;
     const int n_tiles = (t1 - t0 + tile - 1) / tile;
+    // a warp fetches a token at a time; `wide`: every run starts on a 16-byte boundary and is a multiple of four
     auto fetch = [&](int k) {
         float* buf = sm + (size_t)(k & 1) * tile * rl;
         const int first = t0 + k * tile, n = min(tile, t1 - first);
-        const int items = 4 * d + cols;
-        for (int idx = threadIdx.x; idx < n * items; idx += blockDim.x) {
-            const int tok = idx / items, i = idx - tok * items;
-            const float* row = proj + (long long)(first + tok) * ld;
-            float* dst = buf + (size_t)tok * rl + i;
-            if (i < d) copy4_async(dst, row + off_r + hd + i);
-            else if (i < 2 * d) copy4_async(dst, row + off_k + hd + (i - d));
-            else if (i < 3 * d) copy4_async(dst, row + off_a + hd + (i - 2 * d));
-            else if (i < 4 * d) copy4_async(dst, lw + (long long)(first + tok) * ldlw + hd + (i - 3 * d));
-            else if (j0 + (i - 4 * d) < d) copy4_async(dst, row + off_v + hd + j0 + (i - 4 * d));
+        const int lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
+        for (int tok = threadIdx.x >> 5; tok < n; tok += nwarp) {
+            const float* row = proj + (long long)(first + tok) * ld + hd;
+            const float* srcW = lw + (long long)(first + tok) * ldlw + hd;
+            float* dst = buf + (size_t)tok * rl;
+            const int nv = min(cols, d - j0);
+            if (wide) {
+                for (int i = 4 * lane; i < d; i += 128) {
+                    copy16_async(dst + i, row + off_r + i);
+                    copy16_async(dst + d + i, row + off_k + i);
+                    copy16_async(dst + 2 * d + i, row + off_a + i);
+                    copy16_async(dst + 3 * d + i, srcW + i);
+                }
+                for (int i = 4 * lane; i < nv; i += 128) copy16_async(dst + 4 * d + i, row + off_v + j0 + i);
+            } else {
+                for (int i = lane; i < d; i += 32) {
+                    copy4_async(dst + i, row + off_r + i);
+                    copy4_async(dst + d + i, row + off_k + i);
+                    copy4_async(dst + 2 * d + i, row + off_a + i);
+                    copy4_async(dst + 3 * d + i, srcW + i);
+                }
+                for (int i = lane; i < nv; i += 32) copy4_async(dst + 4 * d + i, row + off_v + j0 + i);
+            }
         }
         copies_commit();
     };
@@ -609,13 +640,16 @@ void ssm_scan(const float* xbc, int ldx, const float* dt_raw, int lddt, const fl
     const size_t smem = 2 * (size_t)tile * rl * sizeof(float);
     DLM_CHECK(smem <= 200 * 1024, "ssm_scan: a token's inputs do not fit in shared memory");
     const dim3 grid(heads, R, chunks);
+    // 16-byte copies: every run of a token's inputs starts on a 16-byte boundary and is a multiple of four floats
+    const int wide = (reinterpret_cast<uintptr_t>(xbc) % 16 == 0 && ldx % 4 == 0 && N % 4 == 0 && P % 4 == 0 &&
+                      cols % 4 == 0 && (heads * P) % 4 == 0) ? 1 : 0;
 #define DLM_SSM(NPT, V)                                                                                               \
     do {                                                                                                              \
         if (smem > 48 * 1024)                                                                                         \
             cudaFuncSetAttribute(ssm_scan_kernel<NPT, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
         ssm_scan_kernel<NPT, V><<<grid, cols * parts, smem, stream>>>(xbc, ldx, dt_raw, lddt, dt_bias, A_log, D, state, \
                                                                      cu_q, state_slot, y, heads, P, N, groups, parts, \
-                                                                     tile);                                           \
+                                                                     tile, wide);                                     \
     } while (0)
     if (vec) {
         if (per <= 4) DLM_SSM(4, true);
@@ -645,13 +679,16 @@ void delta_scan(const float* proj, int ld, int off_r, int off_k, int off_v, int 
     const size_t smem = 2 * (size_t)tile * rl * sizeof(float);
     DLM_CHECK(smem <= 200 * 1024, "delta_scan: a token's inputs do not fit in shared memory");
     const dim3 grid(heads, R, chunks);
+    const int wide = (reinterpret_cast<uintptr_t>(proj) % 16 == 0 && reinterpret_cast<uintptr_t>(lw) % 16 == 0 &&
+                      ld % 4 == 0 && ldlw % 4 == 0 && d % 4 == 0 && cols % 4 == 0 && off_r % 4 == 0 && off_k % 4 == 0 &&
+                      off_v % 4 == 0 && off_a % 4 == 0) ? 1 : 0;
 #define DLM_DELTA(NPT, V)                                                                                             \
     do {                                                                                                              \
         if (smem > 48 * 1024)                                                                                         \
             cudaFuncSetAttribute(delta_scan_kernel<NPT, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
         delta_scan_kernel<NPT, V><<<grid, cols * parts, smem, stream>>>(proj, ld, off_r, off_k, off_v, off_a, lw, ldlw, \
                                                                        a_bias, state, cu_q, state_slot, o, heads, d,  \
-                                                                       unit_eps, decay_coef, parts, tile);            \
+                                                                       unit_eps, decay_coef, parts, tile, wide);      \
     } while (0)
     if (vec) {
         if (per <= 4) DLM_DELTA(4, true);
