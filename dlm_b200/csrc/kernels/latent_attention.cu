@@ -30,6 +30,8 @@ __global__ void latent_prep_kernel(const float* __restrict__ proj, int ld, int o
                                    int dr, const float* __restrict__ inv_freq, int rot_dims,
                                    const int32_t* __restrict__ positions, const int32_t* __restrict__ slots, float eps,
                                    T* cq_out, T* cache, int page_size, int total_pages, int* err) {
+    dep_wait();          // nothing is read or written before the kernels before this one have ended
+    dep_launch_next();
     __shared__ float s_part[32];
     const int t = blockIdx.x;
     const float* row = proj + (long long)t * ld;
@@ -90,6 +92,8 @@ template <typename T>
 __global__ void latent_q_split_kernel(const float* __restrict__ q, int ldq, const int32_t* __restrict__ positions,
                                       const float* __restrict__ inv_freq, int rot_dims, T* qn, float* qr, int Tn, int H,
                                       int dn, int dr) {
+    dep_wait();          // nothing is read or written before the kernels before this one have ended
+    dep_launch_next();
     const int t = blockIdx.x;
     const int half = rot_dims / 2;
     const float pos = (float)positions[t];
@@ -123,6 +127,8 @@ __global__ void latent_q_split_kernel(const float* __restrict__ q, int ldq, cons
 template <typename T>
 __global__ void latent_gate_out_kernel(const float* __restrict__ val, const float* __restrict__ gate, int ldg, T* out,
                                        int Tn, int H, int dv) {
+    dep_wait();          // nothing is read or written before the kernels before this one have ended
+    dep_launch_next();
     const int t = blockIdx.x;
     for (int idx = threadIdx.x; idx < H * dv; idx += blockDim.x) {
         const int h = idx / dv, d = idx - h * dv;
@@ -146,6 +152,9 @@ latent_attention_kernel(const float* __restrict__ q_lat, const float* __restrict
                         const int32_t* __restrict__ token_req, const int32_t* __restrict__ positions, T* lat,
                         float* partial, int Tn, int H, int dr, int rank, int page_size, int total_pages, int window,
                         float scale, int hg_max, int n_splits, int* err) {
+    dep_wait();          // nothing is read or written before the kernels before this one have ended
+    // (a long kernel, launched in the ordinary way: its blocks are placed when the machine is free, and the
+    // kernel after it is let in only when it ends)
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int width = rank + dr;
     const int wpad = (width + 7) & ~7;                      // row pitch of the staged keys (16-byte multiples)
@@ -317,7 +326,8 @@ latent_attention_kernel(const float* __restrict__ q_lat, const float* __restrict
 
 // The same on tensor cores (bfloat16, latent size a multiple of 128 up to 512): one block a (token, up to 16 heads,
 // split).  The heads are the 16 rows of m16n8k16 products.  Per chunk of 32 keys: scores S[16 x 32] = Q K^T over the
-// whole row [c | k_rot] (zero-padded to a multiple of 64), warp w taking keys 8 (w % 4) .. and half of the k range;
+// whole row [c | k_rot] (zero-padded to a multiple of 64; the rows of the next chunk arrive by asynchronous copies
+// meanwhile), warp w taking keys 8 (w % 4) .. and half of the k range;
 // the two halves meet in shared memory where warp w takes the softmax step of rows w and w + 8 in 32-bit; the weights
 // go back as two bfloat16 terms (p = hi + lo, so that the 32-bit weights lose nothing in the product); then
 // O[16 x rank] += P C with warp w owning 8 NT latent columns, its accumulators in registers for the whole walk.
@@ -333,14 +343,17 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __rest
                             const int32_t* __restrict__ token_req, const int32_t* __restrict__ positions,
                             __nv_bfloat16* lat, float* partial, int Tn, int H, int dr, int rank, int page_size,
                             int total_pages, int window, float scale, int n_splits, int* err) {
+    dep_wait();          // nothing is read or written before the kernels before this one have ended
+    // (a long kernel, launched in the ordinary way: its blocks are placed when the machine is free, and the
+    // kernel after it is let in only when it ends)
     typedef __nv_bfloat16 bf16;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int width = rank + dr;
     const int wk = (width + 63) & ~63;                      // k extent of the score product
     const int qp = wk + 8;                                  // row pitch: 16 bytes off a multiple of 128
     bf16* s_q = reinterpret_cast<bf16*>(smem_raw);          // [16][qp]  queries [through W_uk | rotated part]
-    bf16* s_keys = s_q + (size_t)LM_ROWS * qp;              // [32][qp]  the chunk's cache rows
-    bf16* s_pb = s_keys + (size_t)LA_KC * qp;               // [2][16][LM_PP] weights, high and low term
+    bf16* s_keys0 = s_q + (size_t)LM_ROWS * qp;             // [2][32][qp]  the cache rows of this chunk and the next
+    bf16* s_pb = s_keys0 + (size_t)2 * LA_KC * qp;          // [2][16][LM_PP] weights, high and low term
     float* s_s = reinterpret_cast<float*>(s_pb + 2 * LM_ROWS * LM_PP);   // [2][16][32] scores of the two k halves
     float* s_m = s_s + 2 * LM_ROWS * LA_KC;                 // [16]
     float* s_l = s_m + LM_ROWS;
@@ -361,9 +374,9 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __rest
         }
         s_q[idx] = __float2bfloat16_rn(v);
     }
-    for (int idx = threadIdx.x; idx < LA_KC * (qp - width); idx += LA_THREADS) {     // the padding stays zero
+    for (int idx = threadIdx.x; idx < 2 * LA_KC * (qp - width); idx += LA_THREADS) {     // the padding stays zero
         const int row = idx / (qp - width), c = idx - row * (qp - width);
-        s_keys[(size_t)row * qp + width + c] = __float2bfloat16_rn(0.f);
+        s_keys0[(size_t)row * qp + width + c] = __float2bfloat16_rn(0.f);
     }
     if (threadIdx.x < LM_ROWS) {
         s_m[threadIdx.x] = -INFINITY;
@@ -381,11 +394,12 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __rest
     const int c_begin = c_first + ks_id * per, c_end = min(c_begin + per, c_last + 1);
     const int arow = (lane & 7) + 8 * ((lane >> 3) & 1);    // the row a lane names in a 16-row ldmatrix.x4
     const int n_base = warp * NT * 8;
-    for (int ch = c_begin; ch < c_end; ++ch) {
-        __syncthreads();                                    // the chunk before is done with s_keys, s_s and s_pb
+    // the rows of chunk `ch` into buffer `which`: asynchronous 16-byte copies (zeros where the token sees no key)
+    auto stage = [&](int ch, int which) {
+        bf16* base = s_keys0 + (size_t)which * LA_KC * qp;
         for (int jj = warp; jj < LA_KC; jj += LA_THREADS / 32) {
             const int j = ch * LA_KC + jj;
-            bf16* dst = s_keys + (size_t)jj * qp;
+            bf16* dst = base + (size_t)jj * qp;
             const bf16* row = nullptr;
             if (j >= lo && j <= p) {
                 const int lp = j / page_size;
@@ -396,13 +410,24 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __rest
                     row = cache + ((long long)page * page_size + (j - lp * page_size)) * width;
                 }
             }
-            uint4* d4 = reinterpret_cast<uint4*>(dst);
             if (row == nullptr) {
+                uint4* d4 = reinterpret_cast<uint4*>(dst);
                 for (int i = lane; i < width / 8; i += 32) d4[i] = make_uint4(0u, 0u, 0u, 0u);
             } else {
-                const uint4* src = reinterpret_cast<const uint4*>(row);
-                for (int i = lane; i < width / 8; i += 32) d4[i] = src[i];
+                for (int i = lane; i < width / 8; i += 32) cp_async16(dst + 8 * i, row + 8 * i);
             }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    if (c_begin < c_end) stage(c_begin, 0);
+    for (int ch = c_begin; ch < c_end; ++ch) {
+        const bf16* s_keys = s_keys0 + (size_t)((ch - c_begin) & 1) * LA_KC * qp;
+        __syncthreads();                                    // the chunk before is done with the other buffer, s_s and s_pb
+        if (ch + 1 < c_end) {
+            stage(ch + 1, (ch + 1 - c_begin) & 1);          // the next chunk comes in while this one is worked on
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
         __syncthreads();
         // ---- scores: keys 8 nt .. 8 nt + 7, one half of the k range
@@ -513,6 +538,8 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const float* __rest
 template <typename T>
 __global__ void latent_merge_kernel(const float* __restrict__ partial, int n_splits, const float* __restrict__ sink,
                                     T* lat, int Tn, int H, int rank) {
+    dep_wait();          // nothing is read or written before the kernels before this one have ended
+    dep_launch_next();
     const int t = blockIdx.x, h = blockIdx.y;
     const float* base = partial + ((long long)t * H + h) * n_splits * (rank + 2);
     const float snk = sink ? sink[h] : -INFINITY;
@@ -545,11 +572,11 @@ void latent_prep(const float* proj, int ld, int off_q, int q_rank, const float* 
     DLM_CHECK(rot_dims % 2 == 0 && rot_dims >= 0 && rot_dims <= dr, "latent_prep: rotated dims must be even and <= dr");
     int* err = error_flag_ptr();
     if (dtype == F32)
-        latent_prep_kernel<float><<<T, 128, 0, stream>>>(proj, ld, off_q, q_rank, qn_w, off_kv, rank, kvn_w, dr, inv_freq,
+        launch_dep(latent_prep_kernel<float>, dim3(T), dim3(128), 0, stream, proj, ld, off_q, q_rank, qn_w, off_kv, rank, kvn_w, dr, inv_freq,
                                                         rot_dims, positions, slots, eps, static_cast<float*>(cq_out),
                                                         static_cast<float*>(cache), page_size, total_pages, err);
     else
-        latent_prep_kernel<__nv_bfloat16><<<T, 128, 0, stream>>>(
+        launch_dep(latent_prep_kernel<__nv_bfloat16>, dim3(T), dim3(128), 0, stream, 
             proj, ld, off_q, q_rank, qn_w, off_kv, rank, kvn_w, dr, inv_freq, rot_dims, positions, slots, eps,
             static_cast<__nv_bfloat16*>(cq_out), static_cast<__nv_bfloat16*>(cache), page_size, total_pages, err);
     check_launch("latent_prep");
@@ -583,7 +610,7 @@ void launch_latent(const float* q_lat, const float* q_rot, const float* sink, co
         error_flag_ptr());
     check_launch("latent_attention");
     if (n_splits > 1) {
-        latent_merge_kernel<T><<<dim3(Tn, H), 128, 0, stream>>>(partial, n_splits, sink, static_cast<T*>(lat), Tn, H, rank);
+        launch_dep(latent_merge_kernel<T>, dim3(Tn, H), dim3(128), 0, stream, partial, n_splits, sink, static_cast<T*>(lat), Tn, H, rank);
         check_launch("latent_merge");
     }
 }
@@ -617,10 +644,10 @@ void latent_q_split(const float* q, int ldq, const int32_t* positions, const flo
     if (T <= 0) return;
     DLM_CHECK(rot_dims % 2 == 0 && rot_dims >= 0 && rot_dims <= dr, "latent_q_split: rotated dims must be even and <= dr");
     if (dtype == F32)
-        latent_q_split_kernel<float><<<T, 256, 0, stream>>>(q, ldq, positions, inv_freq, rot_dims, static_cast<float*>(qn),
+        launch_dep(latent_q_split_kernel<float>, dim3(T), dim3(256), 0, stream, q, ldq, positions, inv_freq, rot_dims, static_cast<float*>(qn),
                                                            qr, T, H, dn, dr);
     else
-        latent_q_split_kernel<__nv_bfloat16><<<T, 256, 0, stream>>>(q, ldq, positions, inv_freq, rot_dims,
+        launch_dep(latent_q_split_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, q, ldq, positions, inv_freq, rot_dims,
                                                                    static_cast<__nv_bfloat16*>(qn), qr, T, H, dn, dr);
     check_launch("latent_q_split");
 }
@@ -629,9 +656,9 @@ void latent_gate_out(const float* val, const float* gate, int ldg, void* out, in
                      cudaStream_t stream) {
     if (T <= 0) return;
     if (dtype == F32)
-        latent_gate_out_kernel<float><<<T, 256, 0, stream>>>(val, gate, ldg, static_cast<float*>(out), T, H, dv);
+        launch_dep(latent_gate_out_kernel<float>, dim3(T), dim3(256), 0, stream, val, gate, ldg, static_cast<float*>(out), T, H, dv);
     else
-        latent_gate_out_kernel<__nv_bfloat16><<<T, 256, 0, stream>>>(val, gate, ldg, static_cast<__nv_bfloat16*>(out), T,
+        launch_dep(latent_gate_out_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, val, gate, ldg, static_cast<__nv_bfloat16*>(out), T,
                                                                     H, dv);
     check_launch("latent_gate_out");
 }
@@ -645,7 +672,7 @@ void latent_attention(const float* q_lat, const float* q_rot, const float* sink,
     DLM_CHECK(n_splits >= 1 && (n_splits == 1 || partial != nullptr), "latent_attention: splits need a scratch buffer");
     if (latent_use_mma(dtype, rank, dr, fast)) {
         const int wk = (rank + dr + 63) & ~63, qp = wk + 8;
-        const size_t smem = ((size_t)(LM_ROWS + LA_KC) * qp + 2 * LM_ROWS * LM_PP) * sizeof(__nv_bfloat16) +
+        const size_t smem = ((size_t)(LM_ROWS + 2 * LA_KC) * qp + 2 * LM_ROWS * LM_PP) * sizeof(__nv_bfloat16) +
                             (2 * LM_ROWS * LA_KC + 3 * LM_ROWS) * sizeof(float);
         const dim3 grid(T, (H + LM_ROWS - 1) / LM_ROWS, n_splits);
 #define DLM_LMMA(NT)                                                                                                  \
@@ -666,7 +693,7 @@ void latent_attention(const float* q_lat, const float* q_rot, const float* sink,
 #undef DLM_LMMA
         check_launch("latent_attention (tensor cores)");
         if (n_splits > 1) {
-            latent_merge_kernel<__nv_bfloat16><<<dim3(T, H), 128, 0, stream>>>(
+            launch_dep(latent_merge_kernel<__nv_bfloat16>, dim3(T, H), dim3(128), 0, stream, 
                 partial, n_splits, sink, static_cast<__nv_bfloat16*>(lat), T, H, rank);
             check_launch("latent_merge");
         }

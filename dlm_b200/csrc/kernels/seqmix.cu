@@ -24,6 +24,8 @@ template <typename T> __device__ __forceinline__ void put(void* base, long long 
 template <typename T>
 __global__ void add_rows_kernel(float* x, const T* __restrict__ table, const int32_t* __restrict__ idx, int H, int rows,
                                 int* err) {
+    dep_wait();          // nothing is read or written before the kernels before this one have ended
+    dep_launch_next();
     const int t = blockIdx.x;
     const int r = idx[t];
     if (r < 0 || r >= rows) {
@@ -37,6 +39,8 @@ __global__ void add_rows_kernel(float* x, const T* __restrict__ table, const int
 
 // ----------------------------------------------------------------- residual streams
 __global__ void streams_expand_kernel(const float* __restrict__ x, float* xs, int S, int H) {
+    dep_wait();          // nothing is read or written before the kernels before this one have ended
+    dep_launch_next();
     const int t = blockIdx.x;
     const float* r = x + (long long)t * H;
     float* o = xs + (long long)t * S * H;
@@ -52,6 +56,8 @@ __global__ void streams_expand_kernel(const float* __restrict__ x, float* xs, in
 template <typename TOut>
 __global__ void streams_reduce_kernel(const float* __restrict__ xs, const float* __restrict__ a,
                                       const float* __restrict__ norm_w, float eps, TOut* out, int S, int H) {
+    dep_wait();          // nothing is read or written before the kernels before this one have ended
+    dep_launch_next();
     extern __shared__ float su[];        // [H]
     __shared__ float s_part[32];
     const int t = blockIdx.x;
@@ -80,6 +86,8 @@ constexpr int MAX_STREAMS = 16;
 template <int SC>
 __global__ void streams_update_kernel(float* xs, const float* __restrict__ mix, const float* __restrict__ outw,
                                       const float* __restrict__ y, int H) {
+    dep_wait();          // nothing is read or written before the kernels before this one have ended
+    dep_launch_next();
     __shared__ float s_mix[SC * SC], s_out[SC];
     for (int i = threadIdx.x; i < SC * SC; i += blockDim.x) s_mix[i] = mix[i];
     for (int i = threadIdx.x; i < SC; i += blockDim.x) s_out[i] = outw[i];
@@ -111,6 +119,8 @@ __global__ void causal_conv_kernel(const float* __restrict__ x, int ldx, const f
                                    const int32_t* __restrict__ cu_q, const int32_t* __restrict__ token_req,
                                    const int32_t* __restrict__ state_slot, int C, int taps, int add_input, int act,
                                    TOut* out, int ldo) {
+    dep_wait();          // nothing is read or written before the kernels before this one have ended
+    dep_launch_next();
     const int t = blockIdx.x;
     const int r = token_req[t];
     const int start = cu_q[r];
@@ -134,6 +144,8 @@ __global__ void causal_conv_kernel(const float* __restrict__ x, int ldx, const f
 constexpr int MAX_TAPS = 16;
 __global__ void conv_state_kernel(const float* __restrict__ x, int ldx, float* state, const int32_t* __restrict__ cu_q,
                                   const int32_t* __restrict__ state_slot, int C, int taps) {
+    dep_wait();          // nothing is read or written before the kernels before this one have ended
+    dep_launch_next();
     const int r = blockIdx.x;
     const int start = cu_q[r], n = cu_q[r + 1] - start;
     const int keep = taps - 1;
@@ -151,6 +163,8 @@ __global__ void conv_state_kernel(const float* __restrict__ x, int ldx, float* s
 // -------------------------------------------------------------------- activations
 template <typename TOut>
 __global__ void activation_kernel(const float* __restrict__ x, int ldx, TOut* out, int ldo, int cols, int op) {
+    dep_wait();          // nothing is read or written before the kernels before this one have ended
+    dep_launch_next();
     const int r = blockIdx.x;
     for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < cols; c += gridDim.y * blockDim.x) {
         const float z = x[(long long)r * ldx + c];
@@ -168,6 +182,8 @@ __global__ void activation_kernel(const float* __restrict__ x, int ldx, TOut* ou
 // ------------------------------------------------------------ experts from a table
 __global__ void table_lookup_kernel(const int32_t* __restrict__ tokens, const int32_t* __restrict__ table, int32_t* ids,
                                     float* wts, int T, int V, int top, int E, int* err) {
+    dep_wait();          // nothing is read or written before the kernels before this one have ended
+    dep_launch_next();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= T * top) return;
     const int t = i / top, j = i - t * top;
@@ -192,6 +208,8 @@ __global__ void table_lookup_kernel(const int32_t* __restrict__ tokens, const in
 template <typename TOut>
 __global__ void gated_rmsnorm_kernel(const float* __restrict__ y, int ldy, const float* __restrict__ gate, int ldg,
                                      const float* __restrict__ w, TOut* out, int ldo, int gs, float eps, int mode) {
+    dep_wait();          // nothing is read or written before the kernels before this one have ended
+    dep_launch_next();
     __shared__ float s_part[32];
     const int t = blockIdx.x, g = blockIdx.y;
     const float* yr = y + (long long)t * ldy + (long long)g * gs;
@@ -243,6 +261,9 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, int ldx, const fl
                                 const float* __restrict__ D, float* state, const int32_t* __restrict__ cu_q,
                                 const int32_t* __restrict__ state_slot, float* y, int heads, int P, int N, int groups,
                                 int parts, int tile, int wide) {
+    dep_wait();          // nothing is read or written before the kernels before this one have ended
+    // (a long kernel, launched in the ordinary way: its blocks are placed when the machine is free, and the
+    // kernel after it is let in only when it ends)
     extern __shared__ __align__(16) float sm[];            // [2][tile][2 N + cols + 2]: B, C, x, dt, decay
     const int h = blockIdx.x, r = blockIdx.y;
     const int cols = blockDim.x / parts;
@@ -370,6 +391,9 @@ __global__ void delta_scan_kernel(const float* __restrict__ proj, int ld, int of
                                   const float* __restrict__ lw, int ldlw, const float* __restrict__ a_bias, float* state,
                                   const int32_t* __restrict__ cu_q, const int32_t* __restrict__ state_slot, float* o,
                                   int heads, int d, float unit_eps, float decay_coef, int parts, int tile, int wide) {
+    dep_wait();          // nothing is read or written before the kernels before this one have ended
+    // (a long kernel, launched in the ordinary way: its blocks are placed when the machine is free, and the
+    // kernel after it is let in only when it ends)
     extern __shared__ __align__(16) float sm[];            // [2][tile][4 d + cols]: r, k, a, w, v
     const int h = blockIdx.x, r = blockIdx.y;
     const int cols = blockDim.x / parts;
@@ -530,14 +554,14 @@ void scan_layout(int rows, int width, int per, int* parts, int* cols, int* chunk
 void add_rows(float* x, const void* table, const int32_t* idx, int T, int H, int rows, int dtype, cudaStream_t stream) {
     if (T <= 0) return;
     int* err = error_flag_ptr();
-    if (dtype == F32) add_rows_kernel<float><<<T, 256, 0, stream>>>(x, static_cast<const float*>(table), idx, H, rows, err);
-    else add_rows_kernel<__nv_bfloat16><<<T, 256, 0, stream>>>(x, static_cast<const __nv_bfloat16*>(table), idx, H, rows, err);
+    if (dtype == F32) launch_dep(add_rows_kernel<float>, dim3(T), dim3(256), 0, stream, x, static_cast<const float*>(table), idx, H, rows, err);
+    else launch_dep(add_rows_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, x, static_cast<const __nv_bfloat16*>(table), idx, H, rows, err);
     check_launch("add_rows");
 }
 
 void streams_expand(const float* x, float* xs, int T, int S, int H, cudaStream_t stream) {
     if (T <= 0) return;
-    streams_expand_kernel<<<T, 256, 0, stream>>>(x, xs, S, H);
+    launch_dep(streams_expand_kernel, dim3(T), dim3(256), 0, stream, x, xs, S, H);
     check_launch("streams_expand");
 }
 
@@ -549,10 +573,10 @@ void streams_reduce(const float* xs, const float* a, const float* norm_w, float 
     DLM_CHECK(smem <= 200 * 1024, "streams_reduce: a row does not fit in shared memory");
     if (out_dtype == F32) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(streams_reduce_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        streams_reduce_kernel<float><<<T, 256, smem, stream>>>(xs, a, norm_w, eps, static_cast<float*>(out), S, H);
+        launch_dep(streams_reduce_kernel<float>, dim3(T), dim3(256), smem, stream, xs, a, norm_w, eps, static_cast<float*>(out), S, H);
     } else {
         if (smem > 48 * 1024) cudaFuncSetAttribute(streams_reduce_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        streams_reduce_kernel<__nv_bfloat16><<<T, 256, smem, stream>>>(xs, a, norm_w, eps, static_cast<__nv_bfloat16*>(out), S, H);
+        launch_dep(streams_reduce_kernel<__nv_bfloat16>, dim3(T), dim3(256), smem, stream, xs, a, norm_w, eps, static_cast<__nv_bfloat16*>(out), S, H);
     }
     check_launch("streams_reduce");
 }
@@ -564,7 +588,7 @@ void streams_update(float* xs, const float* mix, const float* outw, const float*
     const int slices = T >= 2 * sm_count() ? 1 : (H + 255) / 256;
     const dim3 grid(T, slices);
     switch (S) {
-#define DLM_SU(N) case N: streams_update_kernel<N><<<grid, 256, 0, stream>>>(xs, mix, outw, y, H); break;
+#define DLM_SU(N) case N: launch_dep(streams_update_kernel<N>, dim3(grid), dim3(256), 0, stream, xs, mix, outw, y, H); break;
         DLM_SU(1) DLM_SU(2) DLM_SU(3) DLM_SU(4) DLM_SU(5) DLM_SU(6) DLM_SU(7) DLM_SU(8) DLM_SU(9) DLM_SU(10) DLM_SU(11)
         DLM_SU(12) DLM_SU(13) DLM_SU(14) DLM_SU(15) DLM_SU(16)
 #undef DLM_SU
@@ -579,15 +603,15 @@ void causal_conv(const float* x, int ldx, const float* w, const float* bias, flo
     DLM_CHECK(taps >= 1 && taps <= MAX_TAPS, "causal_conv: 1 to 16 taps");
     const int slices = (C + 255) / 256;
     if (out_dtype == F32)
-        causal_conv_kernel<float><<<dim3(T, slices), 256, 0, stream>>>(x, ldx, w, bias, state, cu_q, token_req, state_slot,
+        launch_dep(causal_conv_kernel<float>, dim3(T, slices), dim3(256), 0, stream, x, ldx, w, bias, state, cu_q, token_req, state_slot,
                                                                     C, taps, add_input, act, static_cast<float*>(out), ldo);
     else
-        causal_conv_kernel<__nv_bfloat16><<<dim3(T, slices), 256, 0, stream>>>(
+        launch_dep(causal_conv_kernel<__nv_bfloat16>, dim3(T, slices), dim3(256), 0, stream, 
             x, ldx, w, bias, state, cu_q, token_req, state_slot, C, taps, add_input, act,
             static_cast<__nv_bfloat16*>(out), ldo);
     check_launch("causal_conv");
     if (taps > 1) {
-        conv_state_kernel<<<dim3(R, slices), 256, 0, stream>>>(x, ldx, state, cu_q, state_slot, C, taps);
+        launch_dep(conv_state_kernel, dim3(R, slices), dim3(256), 0, stream, x, ldx, state, cu_q, state_slot, C, taps);
         check_launch("conv_state");
     }
 }
@@ -597,9 +621,9 @@ void activation(const float* x, int ldx, void* out, int ldo, int rows, int cols,
     if (rows <= 0 || cols <= 0) return;
     const int slices = (cols + 255) / 256 > 64 ? 64 : (cols + 255) / 256;
     if (out_dtype == F32)
-        activation_kernel<float><<<dim3(rows, slices), 256, 0, stream>>>(x, ldx, static_cast<float*>(out), ldo, cols, op);
+        launch_dep(activation_kernel<float>, dim3(rows, slices), dim3(256), 0, stream, x, ldx, static_cast<float*>(out), ldo, cols, op);
     else
-        activation_kernel<__nv_bfloat16><<<dim3(rows, slices), 256, 0, stream>>>(x, ldx, static_cast<__nv_bfloat16*>(out),
+        launch_dep(activation_kernel<__nv_bfloat16>, dim3(rows, slices), dim3(256), 0, stream, x, ldx, static_cast<__nv_bfloat16*>(out),
                                                                               ldo, cols, op);
     check_launch("activation");
 }
@@ -608,7 +632,7 @@ void table_lookup(const int32_t* tokens, const int32_t* table, int32_t* ids, flo
                   cudaStream_t stream) {
     if (T <= 0) return;
     const int n = T * top;
-    table_lookup_kernel<<<(n + 255) / 256, 256, 0, stream>>>(tokens, table, ids, wts, T, V, top, E, error_flag_ptr());
+    launch_dep(table_lookup_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, tokens, table, ids, wts, T, V, top, E, error_flag_ptr());
     check_launch("table_lookup");
 }
 
@@ -617,10 +641,10 @@ void gated_rmsnorm(const float* y, int ldy, const float* gate, int ldg, const fl
     if (T <= 0) return;
     const int threads = group_size >= 256 ? 256 : (group_size >= 128 ? 128 : (group_size > 32 ? 64 : 32));
     if (out_dtype == F32)
-        gated_rmsnorm_kernel<float><<<dim3(T, groups), threads, 0, stream>>>(y, ldy, gate, ldg, w, static_cast<float*>(out),
+        launch_dep(gated_rmsnorm_kernel<float>, dim3(T, groups), dim3(threads), 0, stream, y, ldy, gate, ldg, w, static_cast<float*>(out),
                                                                           ldo, group_size, eps, mode);
     else
-        gated_rmsnorm_kernel<__nv_bfloat16><<<dim3(T, groups), threads, 0, stream>>>(
+        launch_dep(gated_rmsnorm_kernel<__nv_bfloat16>, dim3(T, groups), dim3(threads), 0, stream, 
             y, ldy, gate, ldg, w, static_cast<__nv_bfloat16*>(out), ldo, group_size, eps, mode);
     check_launch("gated_rmsnorm");
 }

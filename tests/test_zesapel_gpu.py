@@ -450,3 +450,38 @@ def test_long_greedy_generation_through_scheduler_and_graphs(name, dtype, folder
     assert clear >= sum(news) // 8
     # the longest request decodes alone at the end: its last step's logits against the plain model
     assert float(row_error(last["row"], ref["0"][-1]) / lim["0"][-1]) < 1.0
+
+
+def test_command_line_with_random_weights(tmp_path):
+    """`dlm-b200 generate --random CONFIG.json --save-random DIR`: the architecture is found through the registry,
+    the weights are drawn and written, and the ids printed are the plain model's greedy choices on that folder."""
+    import ast
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg_path, folder = str(tmp_path / "config.json"), str(tmp_path / "model")
+    with open(cfg_path, "w") as f:
+        json.dump(CONFIGS["X"], f)
+    prompts = [[5, 6, 7, 100, 3], [9]]
+    cmd = [sys.executable, os.path.join(root, "bin", "dlm-b200"), "generate", "--random", cfg_path, "--seed", "3",
+           "--save-random", folder, "--max-new-tokens", "6", "--dtype", "float32"]
+    for p in prompts:
+        cmd += ["--prompt", ",".join(str(t) for t in p)]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
+    assert out.returncode == 0, out.stderr[-2000:]
+    lines = [ln for ln in out.stdout.splitlines() if ln.startswith("generated ids:")]
+    assert len(lines) == len(prompts)
+    oracle = plain.PlainZesapel(folder)
+    for p, ln in zip(prompts, lines):
+        ids = ast.literal_eval(ln.split(":", 1)[1].strip())
+        assert len(ids) == 6
+        seq = list(p)
+        for tok in ids:
+            row = oracle.forward(seq)[-1]
+            top2 = torch.topk(row, 2).values
+            spread = float((row - row.mean()).pow(2).mean().sqrt())
+            if float(top2[0] - top2[1]) > 1e-3 * spread:
+                assert int(torch.argmax(row)) == tok
+            seq.append(tok)
