@@ -5,7 +5,8 @@ identity, convolution taps of the size of the direct path, decays between slow a
 size of the scores.  Matrices are stored in bfloat16 (so that a bfloat16 engine and the 64-bit plain
 implementation read the same numbers), tables in int32.
 
-X, Y and Z differ in every size and option; none of the sizes is a power of two unless a kernel's
+X, Y, Z and W differ in every size and option (W: sizes that are multiples of neither 4 nor 8, so that no 16-byte
+path applies; a window of 3; a last layer without feed-forward); none of the sizes is a power of two unless a kernel's
 fast path needs it, and sizes that a config could make equal by accident (dim, rot_dim, vdim; heads
 of the three mixers; state and vdim) are unequal.  Y has one stream, a layer without feed-forward, a
 window equal to a page and a single expert choice; Z has larger heads (128-wide delta heads, 64-wide
@@ -58,6 +59,11 @@ CONFIGS = {
                      _with(_delta(1, 48), _moe(4, 3, 24)),
                      _with(_latent(5, 16, 24, 16, 36, 20, 64, 250000.0, scale=0.2), _moe(4, 3, 24)),
                      _with(_mamba(6, 8, 40, 3, 1, 6), _moe(2, 2, 72))]},
+    "W": {"architecture": "Zesapel", "vocab": 97, "width": 90, "streams": 2, "max_positions": 500,
+          "embedding": {"scale": 0.7}, "norm": {"eps": 2e-5}, "canon": {"taps": 5},
+          "layers": [_with(_delta(5, 18), _moe(2, 2, 34)),
+                     _with(_mamba(3, 30, 10, 3, 2, 3), _moe(2, 2, 34)),
+                     _with(_latent(7, 10, 4, 14, 26, 22, 3, 777.0, dims=2, scale=0.3), None)]},
     "Z": {"architecture": "Zesapel", "vocab": 260, "width": 128, "streams": 2, "max_positions": 1200,
           "embedding": {"scale": 11.3}, "norm": {"eps": 1e-6}, "canon": {"taps": 3},
           "layers": [_with(_delta(2, 128), _moe(6, 2, 64)),
