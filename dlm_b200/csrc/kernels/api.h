@@ -12,7 +12,8 @@ namespace dlmk {
 enum Epilogue : int {
     EPI_STORE = 0,    // out[m, n] = acc (+ bias[n]), stored as the output dtype
     EPI_ADD = 1,      // out[m, n] += acc, out is float32 (the residual stream)
-    EPI_SWIGLU = 2    // out[m, n/2] = silu(acc[m, n]) * acc[m, n+1] for even n (interleaved weight rows)
+    EPI_SWIGLU = 2,   // out[m, n/2] = silu(acc[m, n]) * acc[m, n+1] for even n (interleaved weight rows)
+    EPI_GELU = 3      // out[m, n] = gelu(acc (+ bias[n])) in its exact (erf) form, stored as the output dtype
 };
 
 // out[T, H] (f32) = table[tokens[t], :] * scale

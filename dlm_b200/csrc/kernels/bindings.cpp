@@ -17,6 +17,7 @@ PYBIND11_MODULE(_dlm_kernels, m) {
     m.attr("EPI_STORE") = (int)dlmk::EPI_STORE;
     m.attr("EPI_ADD") = (int)dlmk::EPI_ADD;
     m.attr("EPI_SWIGLU") = (int)dlmk::EPI_SWIGLU;
+    m.attr("EPI_GELU") = (int)dlmk::EPI_GELU;
 
     m.def("embed", [](u64 tokens, u64 table, u64 out, int T, int H, int V, float scale, int dtype, u64 stream) {
         dlmk::embed(ptr<const int32_t>(tokens), ptr<const void>(table), ptr<float>(out), T, H, V, scale, dtype,

@@ -123,7 +123,7 @@ __global__ void __launch_bounds__(THREADS) gemm_simt_kernel(GemmParams p) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const int col = n0 + tx * 4 + j;
-                if (col < p.N) o[col] = from_f32<TOut>(acc[i][j] + (p.bias ? p.bias[col] : 0.f));
+                if (col < p.N) o[col] = from_f32<TOut>(epi_act<EPI>(acc[i][j] + (p.bias ? p.bias[col] : 0.f)));
             }
         }
     }
@@ -135,6 +135,7 @@ void launch(const GemmParams& p, int epilogue, dim3 grid, cudaStream_t stream) {
         case EPI_STORE: gemm_simt_kernel<TIn, TOut, EPI_STORE><<<grid, THREADS, 0, stream>>>(p); break;
         case EPI_ADD: gemm_simt_kernel<TIn, float, EPI_ADD><<<grid, THREADS, 0, stream>>>(p); break;
         case EPI_SWIGLU: gemm_simt_kernel<TIn, TOut, EPI_SWIGLU><<<grid, THREADS, 0, stream>>>(p); break;
+        case EPI_GELU: gemm_simt_kernel<TIn, TOut, EPI_GELU><<<grid, THREADS, 0, stream>>>(p); break;
         default: DLM_CHECK(false, "gemm: unknown epilogue");
     }
 }
@@ -148,7 +149,7 @@ void gemm_simt(const void* a, int lda, const int32_t* a_rows, const void* w, int
     DLM_CHECK(K > 0, "gemm: K must be > 0");
     DLM_CHECK(epilogue != EPI_SWIGLU || N % 2 == 0, "gemm: the SwiGLU epilogue needs an even N");
     DLM_CHECK(epilogue != EPI_ADD || out_dtype == F32, "gemm: the accumulate epilogue needs a float32 output");
-    DLM_CHECK(bias == nullptr || epilogue == EPI_STORE, "gemm: a bias goes with the store epilogue only");
+    DLM_CHECK(bias == nullptr || epilogue == EPI_STORE || epilogue == EPI_GELU, "gemm: a bias goes with a storing epilogue only");
     GemmParams p{a, lda, a_rows, w, ldw, w_expert_stride, expert_offsets, num_experts, bias, out, ldo, M, N, K};
     int m_tiles = (M + BM - 1) / BM;
     if (expert_offsets != nullptr) {

@@ -196,7 +196,7 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_smallm_kernel(SmallParams p) 
                 for (int ss = 0; ss < S; ++ss) v += red[rr * S + ss][row][m];
                 const long long o = (long long)(row0 + m0 + m) * p.ldo + n;
                 if (EPI == EPI_ADD) static_cast<float*>(p.out)[o] += v;
-                else static_cast<TOut*>(p.out)[o] = from_f32<TOut>(v + (p.bias ? p.bias[n] : 0.f));
+                else static_cast<TOut*>(p.out)[o] = from_f32<TOut>(epi_act<EPI>(v + (p.bias ? p.bias[n] : 0.f)));
             }
         }
     }
@@ -207,6 +207,7 @@ void launch_nt(const SmallParams& p, int epilogue, dim3 grid, cudaStream_t strea
     switch (epilogue) {
         case EPI_STORE: launch_dep(gemm_smallm_kernel<NT, EPI_STORE, TOut>, grid, WARPS * 32, 0, stream, p); break;
         case EPI_ADD: launch_dep(gemm_smallm_kernel<NT, EPI_ADD, float>, grid, WARPS * 32, 0, stream, p); break;
+        case EPI_GELU: launch_dep(gemm_smallm_kernel<NT, EPI_GELU, TOut>, grid, WARPS * 32, 0, stream, p); break;
         default: launch_dep(gemm_smallm_kernel<NT, EPI_SWIGLU, TOut>, grid, WARPS * 32, 0, stream, p); break;
     }
 }

@@ -370,7 +370,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_stream_kernel(StreamParams p)
                         for (int ww = 0; ww < CW; ++ww) v += rb[((size_t)ww * 16 + row) * (MP + 1) + m];
                         const long long o = (long long)(out_row0 + m) * p.ldo + n;
                         if (EPI == EPI_ADD) static_cast<float*>(p.out)[o] += v;
-                        else static_cast<TOut*>(p.out)[o] = from_f32<TOut>(v + (p.bias ? p.bias[n] : 0.f));
+                        else static_cast<TOut*>(p.out)[o] = from_f32<TOut>(epi_act<EPI>(v + (p.bias ? p.bias[n] : 0.f)));
                     }
                 }
                 __syncwarp();
@@ -397,6 +397,8 @@ void launch_nt(const StreamParams& p, int grid, int out_dtype, int epilogue, cud
         case EPI_STORE: if (f32) launch_one<NT, NCH, EPI_STORE, float>(p, grid, stream);
                         else launch_one<NT, NCH, EPI_STORE, __nv_bfloat16>(p, grid, stream); break;
         case EPI_ADD: launch_one<NT, NCH, EPI_ADD, float>(p, grid, stream); break;
+        case EPI_GELU: if (f32) launch_one<NT, NCH, EPI_GELU, float>(p, grid, stream);
+                       else launch_one<NT, NCH, EPI_GELU, __nv_bfloat16>(p, grid, stream); break;
         default: if (f32) launch_one<NT, NCH, EPI_SWIGLU, float>(p, grid, stream);
                  else launch_one<NT, NCH, EPI_SWIGLU, __nv_bfloat16>(p, grid, stream); break;
     }

@@ -66,7 +66,7 @@ __device__ __forceinline__ void epilogue_tile(const TcParams& p, float* st, uint
                                               int row_begin, int row_end, int hsel, int lane, bool vec_ok) {
     const int col = colw + lane;
     const bool col_ok = col < p.N;
-    const float bias = (EPI == EPI_STORE && p.bias != nullptr && col_ok) ? p.bias[col] : 0.f;
+    const float bias = ((EPI == EPI_STORE || EPI == EPI_GELU) && p.bias != nullptr && col_ok) ? p.bias[col] : 0.f;
 #pragma unroll 1
     for (int c0 = hsel * CH; c0 < n_mma; c0 += 2 * CH) {
         uint32_t v[CH];
@@ -112,7 +112,7 @@ __device__ __forceinline__ void epilogue_tile(const TcParams& p, float* st, uint
             __syncwarp();
         } else {
 #pragma unroll
-            for (int j = 0; j < CH; ++j) st[j * 33 + lane] = __uint_as_float(v[j]) + bias;
+            for (int j = 0; j < CH; ++j) st[j * 33 + lane] = epi_act<EPI>(__uint_as_float(v[j]) + bias);
             __syncwarp();
             if (EPI == EPI_ADD) {
                 float* o = static_cast<float*>(p.out) + (long long)tok0 * p.ldo + colw;

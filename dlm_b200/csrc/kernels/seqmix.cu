@@ -14,7 +14,6 @@ namespace {
 
 __device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
 __device__ __forceinline__ float softplus_f(float z) { return z > 30.0f ? z : log1pf(expf(z)); }
-__device__ __forceinline__ float gelu_erf_f(float z) { return 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f)); }
 
 template <typename T> __device__ __forceinline__ void put(void* base, long long i, float v) {
     static_cast<T*>(base)[i] = from_f32<T>(v);
@@ -171,7 +170,7 @@ __global__ void activation_kernel(const float* __restrict__ x, int ldx, TOut* ou
         float v;
         switch (op) {
             case 0: v = tanhf(z); break;
-            case 1: v = gelu_erf_f(z); break;
+            case 1: v = gelu_exact_f(z); break;
             case 2: v = silu_f(z); break;
             default: v = z; break;
         }

@@ -329,21 +329,21 @@ class NativeOps:
 
     def grouped_act(self, a, w_up, offsets, rows, act):
         """``act(a[rows] · w_up[e]^T)`` for each expert's rows, in the activation dtype (``act``: see
-        ``activation``)."""
+        ``activation``).  gelu sits in the product's epilogue; other activations are a kernel behind it."""
         E, N, K = w_up.shape
         M = rows.numel()
-        up = torch.empty((M, N), dtype=torch.float32, device=a.device)
+        fused = act == "gelu"
+        out = torch.empty((M, N), dtype=a.dtype if fused else torch.float32, device=a.device)
+        epi = self.k.EPI_GELU if fused else self.k.EPI_STORE
         if (self.fast and self.tc and a.dtype == torch.bfloat16 and 8 * M > 9 * E and K % 8 == 0
                 and a.stride(0) == K):
             gathered = torch.empty((M, K), dtype=a.dtype, device=a.device)
             self.launches += 1
             self.k.gather_rows(_p(a), _p(rows), _p(gathered), M, K, _dt(a.dtype), self._stream())
-            self._gemm(gathered, w_up, up, M, N, K, self.k.EPI_STORE, offsets=offsets, num_experts=E,
-                       w_expert_stride=N * K)
+            self._gemm(gathered, w_up, out, M, N, K, epi, offsets=offsets, num_experts=E, w_expert_stride=N * K)
         else:
-            self._gemm(a, w_up, up, M, N, K, self.k.EPI_STORE, a_rows=rows, offsets=offsets, num_experts=E,
-                       w_expert_stride=N * K)
-        return self.activation(up, act, a.dtype)
+            self._gemm(a, w_up, out, M, N, K, epi, a_rows=rows, offsets=offsets, num_experts=E, w_expert_stride=N * K)
+        return out if fused else self.activation(out, act, a.dtype)
 
     def table_route(self, tokens, table, E):
         """Experts of each token from a table row of its id, each weighted ``1 / top``, grouped by expert:

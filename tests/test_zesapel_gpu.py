@@ -485,3 +485,25 @@ def test_command_line_with_random_weights(tmp_path):
             if float(top2[0] - top2[1]) > 1e-3 * spread:
                 assert int(torch.argmax(row)) == tok
             seq.append(tok)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("T,E,top,K,N", [(3, 4, 2, 64, 96), (200, 6, 2, 128, 256), (40, 16, 2, 256, 512), (17, 3, 1, 90, 34),
+                                         (700, 8, 2, 1024, 1024), (9, 32, 2, 2048, 2048)])
+def test_experts_first_product_with_gelu_in_its_epilogue(ops, dtype, T, E, top, K, N):
+    """`grouped_act(..., "gelu")` on every product kernel the sizes reach (streaming, tcgen05 single and paired,
+    warp-level, FMA) against the plain statement; silu goes through the separate activation kernel."""
+    ref = PlainOps()
+    g = torch.Generator().manual_seed(T + K)
+    h = torch.randn(T, K, generator=g).to(DEV, dtype)
+    w = (torch.randn(E, N, K, generator=g) / math.sqrt(K)).to(DEV, dtype)
+    table = torch.argsort(torch.rand(50, E, generator=g), dim=1)[:, :top].to(DEV, torch.int32).contiguous()
+    toks = torch.randint(0, 50, (T,), generator=g).to(DEV, torch.int32)
+    _, _, offsets, rows, _ = ops.table_route(toks, table, E)
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-4
+    for act in ("gelu", "silu"):
+        got = ops.grouped_act(h, w, offsets, rows, act)
+        want = ref.grouped_act(h.cpu(), w.cpu(), offsets.cpu(), rows.cpu(), act)
+        assert got.dtype == dtype and torch.allclose(got.float().cpu(), want.float(), atol=tol, rtol=tol), act
+    torch.cuda.synchronize()
+    ops.check_errors()
