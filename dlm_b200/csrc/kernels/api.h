@@ -135,6 +135,12 @@ void streams_reduce(const float* xs, const float* a, const float* norm_w, float 
 void streams_update(float* xs, const float* mix, const float* outw, const float* y, int T, int S, int H,
                     cudaStream_t stream);
 
+// streams_update followed by streams_reduce with the next sublayer's weights, in one pass (S <= 8): xs is updated in
+// place and out[t, :] = rmsnorm(sum_r in_next[r] xs_new[t, r, :]) * norm_w (norm_w == nullptr: the sum itself).
+void streams_update_reduce(float* xs, const float* mix, const float* outw, const float* y, const float* in_next,
+                           const float* norm_w, float eps, void* out, int T, int S, int H, int out_dtype,
+                           cudaStream_t stream);
+
 // Causal convolution over time on each channel, per request, with the request's last taps - 1 inputs carried in
 // state[slots, taps - 1, C] (f32, zero at a request's start) and brought up to date by the call:
 // out[t, c] = (add_input ? x[t, c] : 0) + bias[c] + sum_j w[c, j] x[t - taps + 1 + j, c]; act 1: silu of that.

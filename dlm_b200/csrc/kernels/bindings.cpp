@@ -109,6 +109,12 @@ PYBIND11_MODULE(_dlm_kernels, m) {
         dlmk::streams_update(ptr<float>(xs), ptr<const float>(mix), ptr<const float>(outw), ptr<const float>(y), T, S, H,
                              st(stream));
     });
+    m.def("streams_update_reduce", [](u64 xs, u64 mix, u64 outw, u64 y, u64 in_next, u64 norm_w, float eps, u64 out, int T,
+                                      int S, int H, int out_dtype, u64 stream) {
+        dlmk::streams_update_reduce(ptr<float>(xs), ptr<const float>(mix), ptr<const float>(outw), ptr<const float>(y),
+                                    ptr<const float>(in_next), ptr<const float>(norm_w), eps, ptr<void>(out), T, S, H,
+                                    out_dtype, st(stream));
+    });
     m.def("causal_conv", [](u64 x, int ldx, u64 w, u64 bias, u64 state, u64 cu_q, u64 token_req, u64 state_slot, int T,
                             int R, int C, int taps, int add_input, int act, u64 out, int ldo, int out_dtype, u64 stream) {
         dlmk::causal_conv(ptr<const float>(x), ldx, ptr<const float>(w), ptr<const float>(bias), ptr<float>(state),

@@ -108,6 +108,53 @@ __global__ void streams_update_kernel(float* xs, const float* __restrict__ mix, 
     }
 }
 
+// The update of one sublayer and the read of the next in one pass over the streams: xs is updated as above, and
+// out = rmsnorm(sum_r in_next[r] xs_new[t, r, :]) * norm_w (norm_w == nullptr: the sum itself).  One block a token.
+template <int SC, typename TOut>
+__global__ void streams_update_reduce_kernel(float* xs, const float* __restrict__ mix, const float* __restrict__ outw,
+                                             const float* __restrict__ y, const float* __restrict__ in_next,
+                                             const float* __restrict__ norm_w, float eps, TOut* out, int H) {
+    dep_wait();          // nothing is read or written before the kernels before this one have ended
+    dep_launch_next();
+    extern __shared__ float su[];        // [H]
+    __shared__ float s_mix[SC * SC], s_out[SC], s_in[SC], s_part[32];
+    for (int i = threadIdx.x; i < SC * SC; i += blockDim.x) s_mix[i] = mix[i];
+    for (int i = threadIdx.x; i < SC; i += blockDim.x) {
+        s_out[i] = outw[i];
+        s_in[i] = in_next[i];
+    }
+    __syncthreads();
+    const int t = blockIdx.x;
+    float* r = xs + (long long)t * SC * H;
+    float part = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float old[SC];
+#pragma unroll
+        for (int s = 0; s < SC; ++s) old[s] = r[(long long)s * H + i];
+        const float yv = y[(long long)t * H + i];
+        float u = 0.f;
+#pragma unroll
+        for (int d = 0; d < SC; ++d) {
+            float v = 0.f;
+#pragma unroll
+            for (int s = 0; s < SC; ++s) v = fmaf(s_mix[s * SC + d], old[s], v);
+            v = fmaf(s_out[d], yv, v);
+            r[(long long)d * H + i] = v;
+            u = fmaf(s_in[d], v, u);
+        }
+        su[i] = u;
+        part = fmaf(u, u, part);
+    }
+    TOut* o = out + (long long)t * H;
+    if (norm_w == nullptr) {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_f32<TOut>(su[i]);
+        return;
+    }
+    const float ss = block_sum(part, s_part);
+    const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_f32<TOut>((su[i] * inv) * norm_w[i]);
+}
+
 // ------------------------------------------------------------- causal convolution
 // out[t, c] = (add_input ? x[t, c] : 0) + bias[c] + sum_j w[c, j] * x[t - taps + 1 + j, c], optionally through silu.
 // Inputs before the first token of this step come from the request's carried inputs, state[slot, taps - 1, C]
@@ -593,6 +640,39 @@ void streams_update(float* xs, const float* mix, const float* outw, const float*
 #undef DLM_SU
     }
     check_launch("streams_update");
+}
+
+namespace {
+template <int SC>
+void launch_update_reduce(float* xs, const float* mix, const float* outw, const float* y, const float* in_next,
+                          const float* norm_w, float eps, void* out, int T, int H, int out_dtype, cudaStream_t stream) {
+    const size_t smem = (size_t)H * sizeof(float);
+    if (out_dtype == F32) {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(streams_update_reduce_kernel<SC, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        launch_dep(streams_update_reduce_kernel<SC, float>, dim3(T), dim3(256), smem, stream, xs, mix, outw, y, in_next,
+                   norm_w, eps, static_cast<float*>(out), H);
+    } else {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(streams_update_reduce_kernel<SC, __nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        launch_dep(streams_update_reduce_kernel<SC, __nv_bfloat16>, dim3(T), dim3(256), smem, stream, xs, mix, outw, y,
+                   in_next, norm_w, eps, static_cast<__nv_bfloat16*>(out), H);
+    }
+}
+}  // namespace
+
+void streams_update_reduce(float* xs, const float* mix, const float* outw, const float* y, const float* in_next,
+                           const float* norm_w, float eps, void* out, int T, int S, int H, int out_dtype,
+                           cudaStream_t stream) {
+    if (T <= 0) return;
+    DLM_CHECK(S >= 1 && S <= 8, "streams_update_reduce: at most 8 residual streams");
+    DLM_CHECK((size_t)H * sizeof(float) <= 200 * 1024, "streams_update_reduce: a row does not fit in shared memory");
+    switch (S) {
+#define DLM_SUR(N) case N: launch_update_reduce<N>(xs, mix, outw, y, in_next, norm_w, eps, out, T, H, out_dtype, stream); break;
+        DLM_SUR(1) DLM_SUR(2) DLM_SUR(3) DLM_SUR(4) DLM_SUR(5) DLM_SUR(6) DLM_SUR(7) DLM_SUR(8)
+#undef DLM_SUR
+    }
+    check_launch("streams_update_reduce");
 }
 
 void causal_conv(const float* x, int ldx, const float* w, const float* bias, float* state, const int32_t* cu_q,

@@ -145,6 +145,19 @@ class NativeOps:
         self.launches += 1
         self.k.streams_update(_p(xs), _p(mix), _p(outw), _p(y), T, S, H, self._stream())
 
+    def streams_update_reduce(self, xs, mix, outw, y, in_next, norm_w, eps, out_dtype):
+        """``streams_update`` and the next sublayer's ``streams_reduce`` in one pass over the streams."""
+        T, S, H = xs.shape
+        if S > 8:
+            self.streams_update(xs, mix, outw, y)
+            return self.streams_reduce(xs, in_next, norm_w, eps, out_dtype)
+        assert mix.shape == (S, S) and outw.shape == (S,) and in_next.shape == (S,) and y.shape == (T, H)
+        out = torch.empty((T, H), dtype=out_dtype, device=xs.device)
+        self.launches += 1
+        self.k.streams_update_reduce(_p(xs), _p(mix), _p(outw), _p(y), _p(in_next), _p(norm_w), float(eps), _p(out), T, S,
+                                     H, _dt(out_dtype), self._stream())
+        return out
+
     # ------------------------------------------- convolutions and recurrences
     def causal_conv(self, x, w, bias, state, batch, add_input, silu, out_dtype):
         """Causal convolution over time per channel and request; ``x`` is 32-bit ``[T, C]`` (may be a column

@@ -136,10 +136,19 @@ class HyperConnectionBlock(Part):
             h = self._read(xs, w_in, self.norm1, rt, rt.dtype)
         y = torch.zeros((T, self.hidden), dtype=torch.float32, device=xs.device)
         self.mixer.forward(h, y, ctx, call)
-        ops.streams_update(xs, w_mix, w_out, y)
-        if self.ffn is not None:
+        if self.ffn is None:
+            ops.streams_update(xs, w_mix, w_out, y)
+        else:
+            # the mixer's update of the streams and the feed-forward's read of them, in one pass where the norm
+            # is an RMS norm
+            rms = self.norm2.fusable_rms()
+            w_in2 = self.hc["hc2"][0]
+            if rms is not None:
+                h = ops.streams_update_reduce(xs, w_mix, w_out, y, w_in2, rms[0], rms[1], rt.dtype)
+            else:
+                ops.streams_update(xs, w_mix, w_out, y)
+                h = self._read(xs, w_in2, self.norm2, rt, rt.dtype)
             w_in, w_mix, w_out = self.hc["hc2"]
-            h = self._read(xs, w_in, self.norm2, rt, rt.dtype)
             y = torch.zeros((T, self.hidden), dtype=torch.float32, device=xs.device)
             self.ffn.forward(h, y, ctx, pre_norm=None)
             ops.streams_update(xs, w_mix, w_out, y)

@@ -54,6 +54,10 @@ class PlainOps:
     def streams_update(self, xs, mix, outw, y):
         xs.copy_(torch.einsum("sr,tsh->trh", mix, xs) + outw[None, :, None] * y[:, None, :])
 
+    def streams_update_reduce(self, xs, mix, outw, y, in_next, norm_w, eps, out_dtype):
+        self.streams_update(xs, mix, outw, y)
+        return self.streams_reduce(xs, in_next, norm_w, eps, out_dtype)
+
     # ------------------------------------------- convolutions and recurrences
     def causal_conv(self, x, w, bias, state, batch, add_input, silu, out_dtype):
         T, C = x.shape

@@ -81,6 +81,12 @@ def test_streams_and_positions(ops):
     ref.streams_update(want, mix, outw, y)
     ops.streams_update(xs, mix, outw, y)
     assert torch.allclose(xs, want, rtol=1e-5, atol=1e-5)
+    # the update and the next sublayer's read in one pass
+    for norm_w in (None, w):
+        a1, a2 = xs.clone(), xs.clone()
+        got = ops.streams_update_reduce(a1, mix, outw, y, a, norm_w, 1e-5, torch.float32)
+        want_h = ref.streams_update_reduce(a2, mix, outw, y, a, norm_w, 1e-5, torch.float32)
+        assert torch.allclose(a1, a2, rtol=1e-5, atol=1e-5) and torch.allclose(got, want_h, rtol=1e-4, atol=1e-4)
     with pytest.raises(Exception):
         ops.add_rows(x, table, idx + 50)          # a position beyond the table: reported, not read
         torch.cuda.synchronize()
