@@ -228,3 +228,23 @@ def test_replay_program_on_the_stand_in(folders, tmp_path, monkeypatch):
                 assert float(row_error(torch.from_numpy(rows[k].copy()), ref[fed[e["id"]] + w])) < TOL["float32"]
                 k += 1
             fed[e["id"]] += len(e["tokens"])
+
+
+@pytest.mark.parametrize("kinds", [("delta", "ssm"), ("latent", "latent"), ("ssm",)])
+def test_models_of_one_kind_of_mixer(kinds, tmp_path):
+    """A model without any paged cache (recurrent layers only: tokens are still counted against the pool), one
+    without any recurrent state, and a single layer; canon taps of 1 (no carried inputs at all)."""
+    from zesapel_models import _delta, _latent, _mamba, _moe
+    layer = {"delta": _delta(2, 12), "ssm": _mamba(2, 12, 8, 1, 2, 1),
+             "latent": _latent(2, 8, 4, 12, 16, 12, 5, 100.0, scale=0.3)}
+    cfg = one_layer(layer[kinds[0]], width=32, vocab=41, streams=2, taps=1, mlp=_moe(3, 2, 16))
+    cfg["layers"] += [dict(layer[k], mlp=None) for k in kinds[1:]]
+    folder = str(tmp_path / "m")
+    oracle = plain.PlainZesapel(cfg, write_model(cfg, folder, seed=5))
+    reqs = {"a": tokens(1, 40, 41), "b": tokens(2, 7, 41)}
+    ref = {rid: oracle.forward(t) for rid, t in reqs.items()}
+    eng = cpu_engine(folder)
+    mixed, _ = cuttings.mixed(reqs, max_live=2, seed=6)
+    for steps in (cuttings.whole(reqs), cuttings.portions(reqs, sizes=(2, 5)), mixed):
+        got = cuttings.run_trace(eng, steps)
+        assert max(float(row_error(row, ref[rid][p])) for (rid, p), row in got.items()) < TOL["float32"]

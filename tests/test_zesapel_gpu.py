@@ -357,10 +357,11 @@ LAYERS = {"state_space": _mamba(3, 24, 16, 3, 4, 2), "latent": _latent(3, 24, 16
 
 
 @pytest.mark.parametrize("kind", list(LAYERS))
-@pytest.mark.parametrize("mlp", [None, _moe(4, 2, 24)])
-def test_each_mixer_alone(kind, mlp, tmp_path):
-    """A model of one layer: the mixer (and the experts) alone, whole, token by token, and in portions of two."""
-    cfg = one_layer(LAYERS[kind], mlp=mlp)
+@pytest.mark.parametrize("mlp,taps", [(None, 3), (_moe(4, 2, 24), 3), (_moe(4, 2, 24), 1)])
+def test_each_mixer_alone(kind, mlp, taps, tmp_path):
+    """A model of one layer: the mixer (and the experts) alone, whole, token by token, and in portions of two;
+    also with an input convolution of a single tap (nothing carried from step to step)."""
+    cfg = one_layer(LAYERS[kind], mlp=mlp, taps=taps)
     tensors = write_model(cfg, str(tmp_path / "m"), seed=11)
     oracle = plain.PlainZesapel(cfg, tensors)
     reqs = {"a": tokens(1, 45, cfg["vocab"])}
