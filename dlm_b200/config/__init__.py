@@ -1,5 +1,6 @@
 from .base import ConfigError, read_config_json
 from .qwen2_moe import Qwen2MoeConfig
+from .zasazen import ZasazenConfig
 from .zesapel import ZesapelConfig
 
-__all__ = ["ConfigError", "read_config_json", "Qwen2MoeConfig", "ZesapelConfig"]
+__all__ = ["ConfigError", "read_config_json", "Qwen2MoeConfig", "ZasazenConfig", "ZesapelConfig"]

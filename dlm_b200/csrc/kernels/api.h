@@ -54,16 +54,20 @@ void rope_kv_write(const float* qkv, const int32_t* positions, const float* inv_
                    int page_size, int total_pages, int dtype, cudaStream_t stream);
 
 // Causal (optionally windowed) attention of every token of the step over its request's paged keys and values.
+// A score is dot * scale - slopes[query head] * (query position - key position); slopes (f32 [nh], made at load,
+// never written by a kernel) == nullptr: no distance term.
 // num_single: how many requests have exactly one query token.  With fast != 0 and a scratch buffer of
 // attention_scratch_floats(...) floats those go to the split-key decode kernel.
 void attention(const void* q, const void* k_cache, const void* v_cache, const int32_t* block_table, int table_width,
                const int32_t* cu_q, const int32_t* kv_len, void* out, int T, int R, int nh, int nkv, int hd,
-               int page_size, int total_pages, int window, float scale, int max_q_len, int max_kv_len,
-               int num_single, float* scratch, int dtype, int fast, cudaStream_t stream);
+               int page_size, int total_pages, int window, float scale, const float* slopes, int max_q_len,
+               int max_kv_len, int num_single, float* scratch, int dtype, int fast, cudaStream_t stream);
 // Floats of scratch the decode kernel needs for a step of R requests whose longest holds max_kv_len tokens.
 size_t attention_scratch_floats(int R, int nh, int nkv, int hd, int max_kv_len);
 
 // Router: logits = h · w^T (32-bit); scores = softmax over E (score_fn 0) or sigmoid of each logit (score_fn 1);
+// score_fn 2: softmax as for 0, but select_bias[E] is the router's own bias and is added to the logits first
+// (it then enters scores and choice alike; with norm != 0 the weights are the softmax over the chosen logits);
 // the k best scores (ties: lower index; with select_bias[E] the choice is made on score + bias and the weight
 // stays the score); norm != 0: the chosen weights are divided by their sum; all are multiplied by `scale`.
 // has_gate: w has E + 1 rows and gate[t] = sigmoid(h · w[E]).  The input h is: activations of the weights' dtype
@@ -149,7 +153,7 @@ void causal_conv(const float* x, int ldx, const float* w, const float* bias, flo
                  const int32_t* token_req, const int32_t* state_slot, int T, int R, int C, int taps, int add_input,
                  int act, void* out, int ldo, int out_dtype, cudaStream_t stream);
 
-// out[r, c] = f(x[r, c]); op 0 tanh, 1 gelu (erf), 2 silu.  x f32, out in out_dtype.
+// out[r, c] = f(x[r, c]); op 0 tanh, 1 gelu (erf), 2 silu, 3 gelu (tanh form), 4 copy.  x f32, out in out_dtype.
 void activation(const float* x, int ldx, void* out, int ldo, int rows, int cols, int op, int out_dtype,
                 cudaStream_t stream);
 
@@ -158,16 +162,20 @@ void table_lookup(const int32_t* tokens, const int32_t* table, int32_t* ids, flo
                   cudaStream_t stream);
 
 // Norm over groups of `group_size` channels with a gate.  mode 0: v = y * silu(gate), out = v / rms(v) * w;
-// mode 1: out = y / rms(y) * w * sigmoid(gate).  y, gate f32 (row strides ldy, ldg), w f32 [groups * group_size].
+// mode 1: out = y / rms(y) * w * sigmoid(gate); mode 2: out = y / rms(y) * w * silu(gate).  y, gate f32 (row strides
+// ldy, ldg), w f32 [groups * group_size] or nullptr (every weight 1).
 void gated_rmsnorm(const float* y, int ldy, const float* gate, int ldg, const float* w, void* out, int ldo, int T,
                    int groups, int group_size, float eps, int mode, int out_dtype, cudaStream_t stream);
 
 // State-space scan.  xbc f32 rows [x: heads * P | B: groups * N | C: groups * N]; dt_raw f32 [T, heads] (row stride
 // lddt); state f32 [slots, heads, N, P]; y f32 [T, heads * P].  Per head (group = head / (heads / groups)):
 // dt = softplus(dt_raw + dt_bias); S <- exp(-exp(A_log) dt) S + dt B x^T; y = S^T C + D x.
+// fixed_decay f32 [heads] != nullptr: S <- fixed_decay[head] S + B x^T instead (step size 1; dt_raw, dt_bias and
+// A_log are not read); D == nullptr: no direct term.  With groups == heads and rows [v | k | q] this is linear
+// attention with a constant decay per head: S <- decay S + k v^T, y = S^T q.
 void ssm_scan(const float* xbc, int ldx, const float* dt_raw, int lddt, const float* dt_bias, const float* A_log,
               const float* D, float* state, const int32_t* cu_q, const int32_t* state_slot, float* y, int R, int heads,
-              int P, int N, int groups, cudaStream_t stream);
+              int P, int N, int groups, const float* fixed_decay, cudaStream_t stream);
 
 // Delta-rule scan.  proj f32 rows hold r, k, v and the raw removal rate at the given column offsets (heads * d
 // each); lw f32 [T, heads * d] the raw decay; state f32 [slots, heads, d, d] (key channel, value channel).
@@ -176,6 +184,41 @@ void ssm_scan(const float* xbc, int ldx, const float* dt_raw, int lddt, const fl
 void delta_scan(const float* proj, int ld, int off_r, int off_k, int off_v, int off_a, const float* lw, int ldlw,
                 const float* a_bias, float* state, const int32_t* cu_q, const int32_t* state_slot, float* o, int R,
                 int heads, int d, float unit_eps, float decay_coef, cudaStream_t stream);
+
+// ---- diagonal state-space scan and mixers that run side by side (scanmix.cu) ----
+
+// Selective scan with a step size per channel and token.  x f32 [T, inner] (after its convolution and activation),
+// dt_raw f32 [T, inner], bc f32 rows [B: N | C: N], z f32 [T, inner] (row strides given); A_log f32 [inner, N],
+// dt_bias and D f32 [inner]; state f32 [slots, inner, N].  Per channel c and state n, with dt = softplus(dt_raw +
+// dt_bias): S[c, n] <- exp(-exp(A_log[c, n]) dt) S[c, n] + dt x_c B_n; y_c = sum_n S[c, n] C_n + D_c x_c;
+// out[t, c] = y_c * silu(z_c) in out_dtype.
+void selective_scan(const float* x, int ldx, const float* dt_raw, int lddt, const float* bc, int ldbc, const float* z,
+                    int ldz, const float* dt_bias, const float* A_log, const float* D, float* state,
+                    const int32_t* cu_q, const int32_t* state_slot, void* out, int ldo, int R, int inner, int N,
+                    int out_dtype, cudaStream_t stream);
+
+// qkv f32 rows [q: nh * d | k: nkv * d | v: nkv * dv] (row stride ld).  q <- q / rms(q over all nh * d entries) * qn_w
+// * (1 + temp_coef * ln(floor((position + 1) / temp_every) + 1)); k likewise with kn_w and no temperature (a weight
+// pointer of nullptr: that projection is not normed; temp_every 0: no temperature).  q goes to q_out[T, nh * D] and,
+// where slots != nullptr and slots[t] >= 0, k and v to the paged caches [pages, nkv, page_size, D], every head D
+// wide with zeros beyond its own size (D >= d, dv).
+void qk_norm_write(const float* qkv, int ld, const int32_t* positions, const float* qn_w, const float* kn_w, float eps,
+                   float temp_coef, int temp_every, const int32_t* slots, void* q_out, void* k_cache, void* v_cache,
+                   int T, int nh, int nkv, int d, int dv, int D, int page_size, int total_pages, int dtype,
+                   cudaStream_t stream);
+
+// Rotary positions in place on f32 rows: two runs of `heads` heads of `dim` entries at columns off_a and off_b; the
+// first rot_dims entries of a head are rotated (entry i with i + rot_dims / 2, angle position * inv_freq[i]), then
+// the whole head is multiplied by the run's factor.
+void rotate_heads(float* x, int ld, const int32_t* positions, const float* inv_freq, int rot_dims, int T, int heads,
+                  int dim, int off_a, float scale_a, int off_b, float scale_b, cudaStream_t stream);
+
+// resid[t, :] += coef * (a[t] / rms(a[t]) * wa + b[t] / rms(b[t]) * wb)   (all f32 [T, H]; b == nullptr: one branch)
+void branch_norm_add(float* resid, const float* a, const float* wa, const float* b, const float* wb, float eps,
+                     float coef, int T, int H, cudaStream_t stream);
+
+// out[t, :] = [a[t, :] | b[t, :]] in out_dtype (a, b f32 [T, H])
+void concat_rows(const float* a, const float* b, void* out, int T, int H, int out_dtype, cudaStream_t stream);
 
 // ---- attention through a cached latent (latent_attention.cu) ----
 

@@ -48,7 +48,7 @@ __global__ void __launch_bounds__(WARPS * 32)
 attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
                         const int32_t* __restrict__ block_table, int table_width, const int32_t* __restrict__ cu_q,
                         const int32_t* __restrict__ kv_len, float* __restrict__ part_o, float* __restrict__ part_ml,
-                        int nh, int nkv, int hd, int page_size, int total_pages, int window, float scale, int chunk,
+                        int nh, int nkv, int hd, int page_size, int total_pages, int window, Score scale, int chunk,
                         int n_splits, int head_passes, int tile, int max_pages, int* err) {
     constexpr int KPW = 32 / LPK;                 // keys per warp per iteration
     constexpr int STREAMS = WARPS * KPW;
@@ -91,12 +91,13 @@ attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
     }
 
     if (j_begin < j_end) {
-        float qv[GT][8];
+        float qv[GT][8], slope[GT];
 #pragma unroll
         for (int g = 0; g < GT; ++g) {
 #pragma unroll
             for (int i = 0; i < 8; ++i) qv[g][i] = 0.f;
             if (g < n_heads && dim_ok) Vec8<T>::load(q + (long long)token * nh * hd + (h0 + g) * hd + d0, qv[g]);
+            slope[g] = (g < n_heads && scale.slopes != nullptr) ? scale.slopes[h0 + g] : 0.f;
         }
         // the pages this block touches
         const int first_page = j_begin / page_size, last_page = (j_end - 1) / page_size;
@@ -173,7 +174,7 @@ attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
                         for (int i = 0; i < 8; ++i) d = fmaf(qv[g][i], kf[u][i], d);
 #pragma unroll
                         for (int o = LPK / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
-                        s[u] = ok[u] ? d * scale : -INFINITY;
+                        s[u] = ok[u] ? d * scale.scale - slope[g] * (float)(p - (j0 + kb + ks + u * STREAMS)) : -INFINITY;
                         mx = fmaxf(mx, s[u]);
                     }
                     if (mx != -INFINITY) {
@@ -257,7 +258,7 @@ template <typename T, int LPK>
 void launch_decode(int gt, dim3 grid, size_t smem_bytes, cudaStream_t stream, const void* q, const void* k_cache,
                    const void* v_cache, const int32_t* block_table, int table_width, const int32_t* cu_q,
                    const int32_t* kv_len, float* part_o, float* part_ml, int nh, int nkv, int hd, int page_size,
-                   int total_pages, int window, float scale, int chunk, int n_splits, int head_passes, int* err) {
+                   int total_pages, int window, Score scale, int chunk, int n_splits, int head_passes, int* err) {
     // a tile of keys is about 16 KB per stage and tensor, and a multiple of the keys a block handles per round
     const int streams = WARPS * (32 / LPK);
     int tile = 16384 / (hd * (int)sizeof(T));
@@ -304,7 +305,7 @@ size_t attention_decode_scratch_floats(int R, int nh, int hd, int n_splits) {
 
 void attention_decode(const void* q, const void* k_cache, const void* v_cache, const int32_t* block_table,
                       int table_width, const int32_t* cu_q, const int32_t* kv_len, void* out, float* scratch, int R,
-                      int nh, int nkv, int hd, int page_size, int total_pages, int window, float scale, int n_splits,
+                      int nh, int nkv, int hd, int page_size, int total_pages, int window, Score scale, int n_splits,
                       int chunk, int dtype, cudaStream_t stream) {
     if (R <= 0) return;
     DLM_CHECK(attention_decode_ok(hd), "decode attention: head_dim must be a multiple of 8, at most 256");

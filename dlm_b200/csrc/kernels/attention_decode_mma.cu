@@ -123,8 +123,8 @@ attention_decode_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* k_cache
                             const __nv_bfloat16* v_cache, const int32_t* __restrict__ block_table,
                             int table_width, const int32_t* __restrict__ cu_q, const int32_t* __restrict__ kv_len,
                             float* part_o, float* part_ml, int nh, int nkv, int page_size,
-                            int page_shift, int total_pages, int window, float scale_log2, int chunk, int n_splits,
-                            int head_passes, __nv_bfloat16* out, int fuse_merge, int* err) {
+                            int page_shift, int total_pages, int window, float scale_log2, const float* __restrict__ slopes,
+                            int chunk, int n_splits, int head_passes, __nv_bfloat16* out, int fuse_merge, int* err) {
     constexpr int PITCH = HD + 8;
     constexpr int KS = HD / 16, DT = HD / 8, CPR = HD / 8;
     dep_wait();
@@ -150,6 +150,9 @@ attention_decode_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* k_cache
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int t = lane & 3;
     const int token = cu_q[r];
+    // rows lane / 4 and lane / 4 + 8 of the tile are query heads h0 + row: their distance terms, in base-2 units
+    const float slope_a = (slopes != nullptr && (lane >> 2) < n_heads) ? slopes[h0 + (lane >> 2)] * 1.4426950408889634f : 0.f;
+    const float slope_b = (slopes != nullptr && (lane >> 2) + 8 < n_heads) ? slopes[h0 + (lane >> 2) + 8] * 1.4426950408889634f : 0.f;
 
     float o[DT][4];
 #pragma unroll
@@ -245,7 +248,8 @@ attention_decode_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* k_cache
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
                         const int j = jw + n * 8 + 2 * t + (c & 1);
-                        const float v = (j >= j_begin && j < j_end) ? s[n][c] * scale_log2 : -INFINITY;
+                        const float v = (j >= j_begin && j < j_end)
+                            ? s[n][c] * scale_log2 - (c < 2 ? slope_a : slope_b) * (float)(p - j) : -INFINITY;
                         s[n][c] = v;
                         if (c < 2) mx_a = fmaxf(mx_a, v); else mx_b = fmaxf(mx_b, v);
                     }
@@ -306,6 +310,7 @@ struct DecodeTmaParams {
     float* part_o; float* part_ml;
     int nh, nkv, page_size, page_shift, total_pages, window;
     float scale_log2;
+    const float* slopes;
     int n_splits, head_passes;
     __nv_bfloat16* out; int fuse_merge;
     int* err;
@@ -344,6 +349,10 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int t = lane & 3;
     const int token = p.cu_q[r];
+    // distance terms of the tile's rows lane / 4 and lane / 4 + 8 (query heads h0 + row), in base-2 units; the table is
+    // made when the model is loaded, no kernel writes it
+    const float slope_a = (p.slopes != nullptr && (lane >> 2) < n_heads) ? p.slopes[h0 + (lane >> 2)] * 1.4426950408889634f : 0.f;
+    const float slope_b = (p.slopes != nullptr && (lane >> 2) + 8 < n_heads) ? p.slopes[h0 + (lane >> 2) + 8] * 1.4426950408889634f : 0.f;
     const int t_begin = (j_begin / BKV) * BKV;
     const int n_tiles = j_begin < j_end ? (j_end - t_begin + BKV - 1) / BKV : 0;
     volatile int* abort_flag = &s_abort;
@@ -440,7 +449,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
                         const int j = jw + n * 8 + 2 * t + (c & 1);
-                        const float v = (j >= j_begin && j < j_end) ? sc[n][c] * p.scale_log2 : -INFINITY;
+                        const float v = (j >= j_begin && j < j_end)
+                            ? sc[n][c] * p.scale_log2 - (c < 2 ? slope_a : slope_b) * (float)(pos - j) : -INFINITY;
                         sc[n][c] = v;
                         if (c < 2) mx_a = fmaxf(mx_a, v); else mx_b = fmaxf(mx_b, v);
                     }
@@ -522,7 +532,7 @@ bool launch_tma(dim3 grid, cudaStream_t stream, const void* k_cache, const void*
 template <int HD>
 void launch(dim3 grid, cudaStream_t stream, const void* q, const void* k_cache, const void* v_cache,
             const int32_t* block_table, int table_width, const int32_t* cu_q, const int32_t* kv_len, float* part_o,
-            float* part_ml, int nh, int nkv, int page_size, int total_pages, int window, float scale, int chunk,
+            float* part_ml, int nh, int nkv, int page_size, int total_pages, int window, Score scale, int chunk,
             int n_splits, int head_passes, void* out, int fuse_merge) {
     size_t smem = (size_t)(ROWS + 4 * BKV) * (HD + 8) * sizeof(__nv_bfloat16);
     const size_t merge = sizeof(float) * (size_t)(2 * WARPS * ROWS + WARPS * ROWS * HD);
@@ -534,7 +544,7 @@ void launch(dim3 grid, cudaStream_t stream, const void* q, const void* k_cache, 
     launch_dep(kern, grid, WARPS * 32, smem, stream,
         static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_cache),
         static_cast<const __nv_bfloat16*>(v_cache), block_table, table_width, cu_q, kv_len, part_o, part_ml, nh, nkv,
-        page_size, shift, total_pages, window, scale * 1.4426950408889634f, chunk, n_splits, head_passes,
+        page_size, shift, total_pages, window, scale.scale * 1.4426950408889634f, scale.slopes, chunk, n_splits, head_passes,
         static_cast<__nv_bfloat16*>(out), fuse_merge, error_flag_ptr());
 }
 
@@ -542,7 +552,7 @@ void launch(dim3 grid, cudaStream_t stream, const void* q, const void* k_cache, 
 
 void attention_decode_mma(const void* q, const void* k_cache, const void* v_cache, const int32_t* block_table,
                           int table_width, const int32_t* cu_q, const int32_t* kv_len, void* out, float* scratch,
-                          int R, int nh, int nkv, int hd, int page_size, int total_pages, int window, float scale,
+                          int R, int nh, int nkv, int hd, int page_size, int total_pages, int window, Score scale,
                           int n_splits, int chunk, cudaStream_t stream) {
     if (R <= 0) return;
     DLM_CHECK(attention_prefill_ok(hd), "decode attention: this head_dim has no tensor-core kernel");
@@ -570,7 +580,8 @@ void attention_decode_mma(const void* q, const void* k_cache, const void* v_cach
         splits = splits < 1 ? 1 : (splits > n_splits ? n_splits : splits);
         const dim3 tma_grid(R, nkv * head_passes, splits);
         DecodeTmaParams p{static_cast<const __nv_bfloat16*>(q), block_table, table_width, cu_q, kv_len, part_o, part_ml, nh,
-                          nkv, page_size, shift, total_pages, window, scale * 1.4426950408889634f, splits, head_passes,
+                          nkv, page_size, shift, total_pages, window, scale.scale * 1.4426950408889634f, scale.slopes, splits,
+                          head_passes,
                           static_cast<__nv_bfloat16*>(out), fuse_merge, error_flag_ptr()};
         // Blocks that have a multiprocessor to themselves keep six tiles in flight instead of three (8 requests
         // of 8,192 tokens: 4.72 -> 4.57 ms a step; of 1,030: 3.245 -> 3.235).

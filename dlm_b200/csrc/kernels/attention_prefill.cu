@@ -34,7 +34,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
                          const __nv_bfloat16* __restrict__ v_cache, const int32_t* __restrict__ block_table,
                          int table_width, const int32_t* __restrict__ cu_q, const int32_t* __restrict__ kv_len,
                          __nv_bfloat16* __restrict__ out, int R, int nh, int nkv, int page_size, int total_pages,
-                         int page_shift, int window, float scale_log2, int skip_single, int n_sm, int* err) {
+                         int page_shift, int window, float scale_log2, const float* __restrict__ slopes, int skip_single, int n_sm,
+                         int* err) {
     constexpr int PITCH = HD + 8;              // elements per shared-memory row (16 bytes of padding)
     constexpr int KS = HD / 16;                // k16 steps over the head dimension
     constexpr int DT = HD / 8;                 // n8 tiles of the output
@@ -54,6 +55,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
     int rank = linear;
     if (linear >= n_sm) rank = linear < 2 * n_sm ? total - 1 - (linear - n_sm) : linear - n_sm;
     const int head = rank % nh, kvh = head / (nh / nkv);
+    // the distance term of a score, in base-2 units like the scale
+    const float slope2 = slopes != nullptr ? slopes[head] * 1.4426950408889634f : 0.f;
     const int bx = (int)gridDim.y - 1 - rank / nh;              // late tiles (most keys) have the low ranks
     if (tid == 0) {
         int acc = 0;
@@ -182,7 +185,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
             // scale (to base 2), mask where needed, running maximum
             float mx_a = m_a, mx_b = m_b;
             const bool all_visible = j0 + BKV - 1 <= w_lo && (window <= 0 || w_hi - j0 < window);
-            if (all_visible) {
+            if (all_visible && slope2 == 0.f) {
 #pragma unroll
                 for (int j = 0; j < BKV / 8; ++j) {
 #pragma unroll
@@ -200,7 +203,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
                         const int key = j0 + j * 8 + 2 * t + (c & 1);
                         const int p = (c < 2) ? pa : pb;
                         const bool vis = key <= p && (window <= 0 || p - key < window);
-                        const float v = vis ? s[j][c] * scale_log2 : -INFINITY;
+                        const float v = vis ? s[j][c] * scale_log2 - slope2 * (float)(p - key) : -INFINITY;
                         s[j][c] = v;
                         if (c < 2) mx_a = fmaxf(mx_a, v); else mx_b = fmaxf(mx_b, v);
                     }
@@ -270,7 +273,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
 template <int HD>
 void launch(dim3 grid, cudaStream_t stream, const void* q, const void* k_cache, const void* v_cache,
             const int32_t* block_table, int table_width, const int32_t* cu_q, const int32_t* kv_len, void* out, int R,
-            int nh, int nkv, int page_size, int total_pages, int window, float scale, int skip_single) {
+            int nh, int nkv, int page_size, int total_pages, int window, Score scale, int skip_single) {
     const size_t smem = (size_t)(BQ + 4 * BKV) * (HD + 8) * sizeof(__nv_bfloat16);
     int shift = -1;
     if ((page_size & (page_size - 1)) == 0) { shift = 0; while ((1 << shift) < page_size) ++shift; }
@@ -280,7 +283,7 @@ void launch(dim3 grid, cudaStream_t stream, const void* q, const void* k_cache, 
         static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_cache),
         static_cast<const __nv_bfloat16*>(v_cache), block_table, table_width, cu_q, kv_len,
         static_cast<__nv_bfloat16*>(out), R, nh, nkv, page_size, total_pages, shift, window,
-        scale * 1.4426950408889634f, skip_single, sm_count(), error_flag_ptr());
+        scale.scale * 1.4426950408889634f, scale.slopes, skip_single, sm_count(), error_flag_ptr());
 }
 
 }  // namespace
@@ -291,7 +294,7 @@ bool attention_prefill_ok(int hd) {
 
 void attention_prefill(const void* q, const void* k_cache, const void* v_cache, const int32_t* block_table,
                        int table_width, const int32_t* cu_q, const int32_t* kv_len, void* out, int T, int R, int nh,
-                       int nkv, int hd, int page_size, int total_pages, int window, float scale, int skip_single,
+                       int nkv, int hd, int page_size, int total_pages, int window, Score scale, int skip_single,
                        cudaStream_t stream) {
     if (T <= 0 || R <= 0) return;
     DLM_CHECK(attention_prefill_ok(hd), "prefill attention: this head_dim has no tensor-core kernel");

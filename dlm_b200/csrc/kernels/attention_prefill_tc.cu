@@ -432,16 +432,17 @@ bool attention_prefill_tc_enabled() {
 }
 
 bool attention_prefill_tc_ok(const void* q, const void* k_cache, const void* v_cache, int nh, int nkv, int hd,
-                             int page_size, float scale) {
-    // (the row maximum is taken before the scores are scaled: the scale must be positive)
-    return scale > 0.f && hd == HD && nkv > 0 && nh % nkv == 0 && page_size >= 64 && (page_size & (page_size - 1)) == 0 &&
+                             int page_size, Score scale) {
+    // (the row maximum is taken before the scores are scaled: the scale must be positive, and a distance term
+    // has no place in that order of steps)
+    return scale.scale > 0.f && scale.slopes == nullptr && hd == HD && nkv > 0 && nh % nkv == 0 && page_size >= 64 && (page_size & (page_size - 1)) == 0 &&
            ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_cache) |
              reinterpret_cast<uintptr_t>(v_cache)) & 15) == 0;
 }
 
 bool attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache, const int32_t* block_table,
                           int table_width, const int32_t* cu_q, const int32_t* kv_len, void* out, int T, int R, int nh,
-                          int nkv, int hd, int page_size, int total_pages, int window, float scale, int skip_single,
+                          int nkv, int hd, int page_size, int total_pages, int window, Score scale, int skip_single,
                           cudaStream_t stream) {
     if (T <= 0 || R <= 0) return true;
     CUtensorMap mq, mk, mv;
@@ -452,7 +453,7 @@ bool attention_prefill_tc(const void* q, const void* k_cache, const void* v_cach
     int shift = 0;
     while ((1 << shift) < page_size) ++shift;
     PrefillTcParams p{block_table, table_width, cu_q, kv_len, static_cast<__nv_bfloat16*>(out), R, nh, nkv, page_size,
-                      shift, total_pages, window, scale * 1.4426950408889634f, skip_single, error_flag_ptr()};
+                      shift, total_pages, window, scale.scale * 1.4426950408889634f, skip_single, error_flag_ptr()};
     const size_t smem = (size_t)TILE_BYTES * 7 + 1024;      // Q, 2 x K, 2 x V, 2 x P, and room to align
     cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     dim3 grid(nh, (T + BQ - 1) / BQ + R);

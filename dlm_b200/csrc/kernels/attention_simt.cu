@@ -26,7 +26,7 @@ __global__ void __launch_bounds__(WARPS * 32)
 attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
                       const int32_t* __restrict__ block_table, int table_width, const int32_t* __restrict__ cu_q,
                       const int32_t* __restrict__ kv_len, T* __restrict__ out, int R, int nh, int nkv, int hd,
-                      int page_size, int total_pages, int window, float scale, int skip_single, int* err) {
+                      int page_size, int total_pages, int window, Score scale, int skip_single, int* err) {
     extern __shared__ float smem[];
     float* Qs = smem;                               // [BQ][hd]
     float* Ks = Qs + BQ * hd;                       // [BKV][hd + 1]
@@ -37,6 +37,7 @@ attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, co
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int head = blockIdx.y;
     const int kvh = head / (nh / nkv);
+    const float slope = scale.slopes != nullptr ? scale.slopes[head] : 0.f;
 
     // which request and which of its query tiles this block has
     if (tid == 0) {
@@ -116,7 +117,7 @@ attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, co
             const float* kr = Ks + lane * (hd + 1);
             float s = 0.f;
             for (int d = 0; d < hd; ++d) s = fmaf(qv[d], kr[d], s);
-            s *= scale;
+            s = s * scale.scale - slope * (float)(p - j);
             const bool visible = (j <= p) && (window <= 0 || p - j < window);
             if (!visible) s = -INFINITY;
             const float m_new = fmaxf(m[i], warp_max(s));
@@ -159,7 +160,7 @@ attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, co
 
 void attention_simt(const void* q, const void* k_cache, const void* v_cache, const int32_t* block_table,
                     int table_width, const int32_t* cu_q, const int32_t* kv_len, void* out, int T, int R, int nh,
-                    int nkv, int hd, int page_size, int total_pages, int window, float scale, int skip_single,
+                    int nkv, int hd, int page_size, int total_pages, int window, Score scale, int skip_single,
                     int dtype, cudaStream_t stream) {
     if (T <= 0 || R <= 0) return;
     DLM_CHECK(hd > 0 && hd <= MAX_HD, "attention: head_dim must be in 1..256");

@@ -43,12 +43,13 @@ PYBIND11_MODULE(_dlm_kernels, m) {
     });
     m.def("attention", [](u64 q, u64 k_cache, u64 v_cache, u64 block_table, int table_width, u64 cu_q, u64 kv_len,
                           u64 out, int T, int R, int nh, int nkv, int hd, int page_size, int total_pages, int window,
-                          float scale, int max_q_len, int max_kv_len, int num_single, u64 scratch, int dtype, int fast,
-                          u64 stream) {
+                          float scale, u64 slopes, int max_q_len, int max_kv_len, int num_single, u64 scratch, int dtype,
+                          int fast, u64 stream) {
         dlmk::attention(ptr<const void>(q), ptr<const void>(k_cache), ptr<const void>(v_cache),
                         ptr<const int32_t>(block_table), table_width, ptr<const int32_t>(cu_q),
                         ptr<const int32_t>(kv_len), ptr<void>(out), T, R, nh, nkv, hd, page_size, total_pages, window,
-                        scale, max_q_len, max_kv_len, num_single, ptr<float>(scratch), dtype, fast, st(stream));
+                        scale, ptr<const float>(slopes), max_q_len, max_kv_len, num_single, ptr<float>(scratch), dtype,
+                        fast, st(stream));
     });
     m.def("attention_scratch_floats", [](int R, int nh, int nkv, int hd, int max_kv_len) {
         return dlmk::attention_scratch_floats(R, nh, nkv, hd, max_kv_len);
@@ -134,10 +135,12 @@ PYBIND11_MODULE(_dlm_kernels, m) {
                             ldo, T, groups, group_size, eps, mode, out_dtype, st(stream));
     });
     m.def("ssm_scan", [](u64 xbc, int ldx, u64 dt_raw, int lddt, u64 dt_bias, u64 A_log, u64 D, u64 state, u64 cu_q,
-                         u64 state_slot, u64 y, int R, int heads, int P, int N, int groups, u64 stream) {
+                         u64 state_slot, u64 y, int R, int heads, int P, int N, int groups, u64 fixed_decay,
+                         u64 stream) {
         dlmk::ssm_scan(ptr<const float>(xbc), ldx, ptr<const float>(dt_raw), lddt, ptr<const float>(dt_bias),
                        ptr<const float>(A_log), ptr<const float>(D), ptr<float>(state), ptr<const int32_t>(cu_q),
-                       ptr<const int32_t>(state_slot), ptr<float>(y), R, heads, P, N, groups, st(stream));
+                       ptr<const int32_t>(state_slot), ptr<float>(y), R, heads, P, N, groups,
+                       ptr<const float>(fixed_decay), st(stream));
     });
     m.def("delta_scan", [](u64 proj, int ld, int off_r, int off_k, int off_v, int off_a, u64 lw, int ldlw, u64 a_bias,
                            u64 state, u64 cu_q, u64 state_slot, u64 o, int R, int heads, int d, float unit_eps,
@@ -145,6 +148,35 @@ PYBIND11_MODULE(_dlm_kernels, m) {
         dlmk::delta_scan(ptr<const float>(proj), ld, off_r, off_k, off_v, off_a, ptr<const float>(lw), ldlw,
                          ptr<const float>(a_bias), ptr<float>(state), ptr<const int32_t>(cu_q),
                          ptr<const int32_t>(state_slot), ptr<float>(o), R, heads, d, unit_eps, decay_coef, st(stream));
+    });
+    m.def("selective_scan", [](u64 x, int ldx, u64 dt_raw, int lddt, u64 bc, int ldbc, u64 z, int ldz, u64 dt_bias, u64 A_log,
+                               u64 D, u64 state, u64 cu_q, u64 state_slot, u64 out, int ldo, int R, int inner, int N,
+                               int out_dtype, u64 stream) {
+        dlmk::selective_scan(ptr<const float>(x), ldx, ptr<const float>(dt_raw), lddt, ptr<const float>(bc), ldbc,
+                             ptr<const float>(z), ldz, ptr<const float>(dt_bias), ptr<const float>(A_log),
+                             ptr<const float>(D), ptr<float>(state), ptr<const int32_t>(cu_q),
+                             ptr<const int32_t>(state_slot), ptr<void>(out), ldo, R, inner, N, out_dtype, st(stream));
+    });
+    m.def("qk_norm_write", [](u64 qkv, int ld, u64 positions, u64 qn_w, u64 kn_w, float eps, float temp_coef,
+                              int temp_every, u64 slots, u64 q_out, u64 k_cache, u64 v_cache, int T, int nh, int nkv,
+                              int d, int dv, int D, int page_size, int total_pages, int dtype, u64 stream) {
+        dlmk::qk_norm_write(ptr<const float>(qkv), ld, ptr<const int32_t>(positions), ptr<const float>(qn_w),
+                            ptr<const float>(kn_w), eps, temp_coef, temp_every, ptr<const int32_t>(slots),
+                            ptr<void>(q_out), ptr<void>(k_cache), ptr<void>(v_cache), T, nh, nkv, d, dv, D, page_size,
+                            total_pages, dtype, st(stream));
+    });
+    m.def("rotate_heads", [](u64 x, int ld, u64 positions, u64 inv_freq, int rot_dims, int T, int heads, int dim,
+                             int off_a, float scale_a, int off_b, float scale_b, u64 stream) {
+        dlmk::rotate_heads(ptr<float>(x), ld, ptr<const int32_t>(positions), ptr<const float>(inv_freq), rot_dims, T,
+                           heads, dim, off_a, scale_a, off_b, scale_b, st(stream));
+    });
+    m.def("branch_norm_add", [](u64 resid, u64 a, u64 wa, u64 b, u64 wb, float eps, float coef, int T, int H,
+                                u64 stream) {
+        dlmk::branch_norm_add(ptr<float>(resid), ptr<const float>(a), ptr<const float>(wa), ptr<const float>(b),
+                              ptr<const float>(wb), eps, coef, T, H, st(stream));
+    });
+    m.def("concat_rows", [](u64 a, u64 b, u64 out, int T, int H, int out_dtype, u64 stream) {
+        dlmk::concat_rows(ptr<const float>(a), ptr<const float>(b), ptr<void>(out), T, H, out_dtype, st(stream));
     });
     m.def("latent_prep", [](u64 proj, int ld, int off_q, int q_rank, u64 qn_w, int off_kv, int rank, u64 kvn_w, int dr,
                             u64 inv_freq, int rot_dims, u64 positions, u64 slots, float eps, u64 cq_out, u64 cache,

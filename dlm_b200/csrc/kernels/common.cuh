@@ -98,6 +98,10 @@ int* error_flag_ptr();
 __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
 // gelu(z) = z (1 + erf(z / sqrt 2)) / 2, the exact form
 __device__ __forceinline__ float gelu_exact_f(float z) { return 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f)); }
+// gelu(z) = z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))) / 2, the tanh form
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+    return 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
+}
 // What a storing epilogue does to acc (+ bias) before it rounds: gelu for EPI (an Epilogue of api.h) == 3, EPI_GELU;
 // nothing otherwise.
 template <int EPI> __device__ __forceinline__ float epi_act(float v) { return EPI == 3 ? gelu_exact_f(v) : v; }

@@ -209,11 +209,14 @@ __device__ __forceinline__ void select_token(float* prob, const float* logits, i
     const int rows = E + (has_gate ? 1 : 0);
     float* pick = prob + (E + 1);                // what the choice is made on (score, or score + bias)
     // COHERENT: the logits were written by other blocks of this launch; read them where those writes are
+    // score_fn 2: the bias is the router's own (logits = h w^T + bias), it enters scores and choice alike
+    const bool router_bias = score_fn == 2 && select_bias != nullptr;
     for (int e = lane; e < rows; e += 32)
-        prob[e] = COHERENT ? __ldcg(logits + (long long)t * rows + e) : logits[(long long)t * rows + e];
+        prob[e] = (COHERENT ? __ldcg(logits + (long long)t * rows + e) : logits[(long long)t * rows + e]) +
+                  (router_bias && e < E ? select_bias[e] : 0.f);
     __syncwarp();
     if (has_gate && lane == 0) gate[t] = 1.0f / (1.0f + expf(-prob[E]));
-    if (score_fn == 0) {
+    if (score_fn == 0 || score_fn == 2) {
         float mx = -INFINITY;
         for (int e = lane; e < E; e += 32) mx = fmaxf(mx, prob[e]);
         mx = warp_max(mx);
@@ -230,7 +233,7 @@ __device__ __forceinline__ void select_token(float* prob, const float* logits, i
     } else {
         for (int e = lane; e < E; e += 32) prob[e] = 1.0f / (1.0f + expf(-prob[e]));
     }
-    for (int e = lane; e < E; e += 32) pick[e] = prob[e] + (select_bias != nullptr ? select_bias[e] : 0.f);
+    for (int e = lane; e < E; e += 32) pick[e] = prob[e] + (select_bias != nullptr && !router_bias ? select_bias[e] : 0.f);
     __syncwarp();
     float chosen_sum = 0.f;
     for (int j = 0; j < k; ++j) {
@@ -496,7 +499,7 @@ void router_topk(const void* h, const void* w, const float* norm_w, float eps, f
                  float* gate, int T, int H, int E, int k, int norm, int has_gate, int dtype, int h_is_f32,
                  int score_fn, float scale, const float* select_bias, int x_settled, cudaStream_t stream) {
     if (T <= 0) return;
-    DLM_CHECK(score_fn == 0 || score_fn == 1, "router: score function must be 0 (softmax) or 1 (sigmoid)");
+    DLM_CHECK(score_fn >= 0 && score_fn <= 2, "router: score function must be 0 (softmax), 1 (sigmoid) or 2 (softmax of biased logits)");
     const bool x32 = norm_w != nullptr || h_is_f32 != 0;      // the activations are 32-bit whatever the weights are
     DLM_CHECK(E >= 1 && k >= 1 && k <= E, "router: top-k must be in 1..num_experts");
     const size_t smem = sizeof(float) * (size_t)H;
@@ -573,7 +576,7 @@ int router_topk_permute(const void* h, const void* w, const float* norm_w, float
         return 3;
     }
     DLM_CHECK(E >= 1 && k >= 1 && k <= E, "router: top-k must be in 1..num_experts");
-    DLM_CHECK(score_fn == 0 || score_fn == 1, "router: score function must be 0 (softmax) or 1 (sigmoid)");
+    DLM_CHECK(score_fn >= 0 && score_fn <= 2, "router: score function must be 0 (softmax), 1 (sigmoid) or 2 (softmax of biased logits)");
     const bool x32 = norm_w != nullptr || h_is_f32 != 0;
     const bool vec = H % 8 == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0;
     if (per_token) {

@@ -219,7 +219,8 @@ __global__ void activation_kernel(const float* __restrict__ x, int ldx, TOut* ou
             case 0: v = tanhf(z); break;
             case 1: v = gelu_exact_f(z); break;
             case 2: v = silu_f(z); break;
-            default: v = z; break;
+            case 3: v = gelu_tanh_f(z); break;
+            default: v = z; break;          // 4: a copy (a change of format)
         }
         out[(long long)r * ldo + c] = from_f32<TOut>(v);
     }
@@ -268,11 +269,13 @@ __global__ void gated_rmsnorm_kernel(const float* __restrict__ y, int ldy, const
     const float ss = block_sum(part, s_part);
     const float inv = 1.0f / sqrtf(ss / (float)gs + eps);
     TOut* o = out + (long long)t * ldo + (long long)g * gs;
-    const float* wr = w + (long long)g * gs;
+    const float* wr = w != nullptr ? w + (long long)g * gs : nullptr;
     for (int i = threadIdx.x; i < gs; i += blockDim.x) {
+        const float wi = wr != nullptr ? wr[i] : 1.0f;
         float v;
-        if (mode == 0) v = ((yr[i] * silu_f(gr[i])) * inv) * wr[i];
-        else v = ((yr[i] * inv) * wr[i]) * sigmoid_f(gr[i]);
+        if (mode == 0) v = ((yr[i] * silu_f(gr[i])) * inv) * wi;
+        else if (mode == 1) v = ((yr[i] * inv) * wi) * sigmoid_f(gr[i]);
+        else v = ((yr[i] * inv) * wi) * silu_f(gr[i]);
         o[i] = from_f32<TOut>(v);
     }
 }
@@ -306,7 +309,7 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, int ldx, const fl
                                 const float* __restrict__ dt_bias, const float* __restrict__ A_log,
                                 const float* __restrict__ D, float* state, const int32_t* __restrict__ cu_q,
                                 const int32_t* __restrict__ state_slot, float* y, int heads, int P, int N, int groups,
-                                int parts, int tile, int wide) {
+                                int parts, int tile, int wide, const float* __restrict__ fixed_decay) {
     dep_wait();          // nothing is read or written before the kernels before this one have ended
     // (a long kernel, launched in the ordinary way: its blocks are placed when the machine is free, and the
     // kernel after it is let in only when it ends)
@@ -329,7 +332,10 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, int ldx, const fl
         const int n = row_of(i);
         s[i] = (live && n < N) ? st[(long long)n * P + p] : 0.f;
     }
-    const float a = -expf(A_log[h]), dcoef = D[h], bias = dt_bias[h];
+    // fixed_decay: the step size is 1 and the head's decay a constant of the model (dt_raw, dt_bias, A_log unused)
+    const bool fixed = fixed_decay != nullptr;
+    const float a = fixed ? 0.f : -expf(A_log[h]), dcoef = D != nullptr ? D[h] : 0.f, bias = fixed ? 0.f : dt_bias[h];
+    const float decay_h = fixed ? fixed_decay[h] : 0.f;
     const int t0 = cu_q[r], t1 = cu_q[r + 1];
     const int n_tiles = (t1 - t0 + tile - 1) / tile;
     // a warp fetches a token at a time; `wide`: every run starts on a 16-byte boundary and is a multiple of four
@@ -357,7 +363,7 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, int ldx, const fl
                 }
                 for (int i = lane; i < nx; i += 32) copy4_async(dst + 2 * N + i, srcX + i);
             }
-            if (lane == 0) copy4_async(dst + 2 * N + cols, dt_raw + (long long)(first + tok) * lddt + h);
+            if (lane == 0 && !fixed) copy4_async(dst + 2 * N + cols, dt_raw + (long long)(first + tok) * lddt + h);
         }
         copies_commit();
     };
@@ -374,9 +380,9 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, int ldx, const fl
         const int first = t0 + k * tile, n = min(tile, t1 - first);
         if (threadIdx.x < n) {
             float* row = buf + (size_t)threadIdx.x * rl;
-            const float dt = softplus_f(row[2 * N + cols] + bias);
+            const float dt = fixed ? 1.0f : softplus_f(row[2 * N + cols] + bias);
             row[2 * N + cols] = dt;
-            row[2 * N + cols + 1] = expf(a * dt);
+            row[2 * N + cols + 1] = fixed ? decay_h : expf(a * dt);
         }
         __syncthreads();
         for (int tok = 0; tok < n; ++tok) {
@@ -730,8 +736,10 @@ void gated_rmsnorm(const float* y, int ldy, const float* gate, int ldg, const fl
 
 void ssm_scan(const float* xbc, int ldx, const float* dt_raw, int lddt, const float* dt_bias, const float* A_log,
               const float* D, float* state, const int32_t* cu_q, const int32_t* state_slot, float* y, int R, int heads,
-              int P, int N, int groups, cudaStream_t stream) {
+              int P, int N, int groups, const float* fixed_decay, cudaStream_t stream) {
     if (R <= 0) return;
+    DLM_CHECK(fixed_decay != nullptr || (dt_raw != nullptr && dt_bias != nullptr && A_log != nullptr && D != nullptr),
+              "ssm_scan: without fixed decays the step sizes, their bias, A_log and D are needed");
     DLM_CHECK(groups >= 1 && heads % groups == 0, "ssm_scan: heads must be a multiple of groups");
     DLM_CHECK(N >= 1 && N <= 1024, "ssm_scan: state size 1..1024");
     int parts, cols, chunks;
@@ -752,7 +760,7 @@ void ssm_scan(const float* xbc, int ldx, const float* dt_raw, int lddt, const fl
             cudaFuncSetAttribute(ssm_scan_kernel<NPT, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
         ssm_scan_kernel<NPT, V><<<grid, cols * parts, smem, stream>>>(xbc, ldx, dt_raw, lddt, dt_bias, A_log, D, state, \
                                                                      cu_q, state_slot, y, heads, P, N, groups, parts, \
-                                                                     tile, wide);                                     \
+                                                                     tile, wide, fixed_decay);                        \
     } while (0)
     if (vec) {
         if (per <= 4) DLM_SSM(4, true);

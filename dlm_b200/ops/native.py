@@ -174,7 +174,7 @@ class NativeOps:
                            _p(out), C, _dt(out_dtype), self._stream())
         return out
 
-    _ACTS = {"tanh": 0, "gelu": 1, "silu": 2}
+    _ACTS = {"tanh": 0, "gelu": 1, "silu": 2, "gelu_tanh": 3, "copy": 4}
 
     def activation(self, x, op, out_dtype):
         """Element-wise ``tanh`` / ``gelu`` (erf) / ``silu`` of 32-bit ``x`` (may be a column slice)."""
@@ -193,20 +193,22 @@ class NativeOps:
         out = torch.empty((T, C), dtype=out_dtype, device=y.device)
         self.launches += 1
         self.k.gated_rmsnorm(_p(y), y.stride(0), _p(gate), gate.stride(0), _p(w), _p(out), C, T, groups, C // groups,
-                             float(eps), {"silu_before": 0, "sigmoid_after": 1}[mode], _dt(out_dtype), self._stream())
+                             float(eps), {"silu_before": 0, "sigmoid_after": 1, "silu_after": 2}[mode], _dt(out_dtype),
+                             self._stream())
         return out
 
-    def ssm_scan(self, xbc, dt_raw, dt_bias, A_log, D, state, batch, heads, P, N, groups):
+    def ssm_scan(self, xbc, dt_raw, dt_bias, A_log, D, state, batch, heads, P, N, groups, fixed_decay=None):
         """State-space scan over each request's tokens; ``state`` ``[slots, heads, N, P]`` is read and left
         up to date.  Returns y ``[T, heads * P]`` in 32-bit."""
         T = xbc.shape[0]
         assert xbc.shape[1] == heads * P + 2 * groups * N and xbc.dtype == torch.float32 and xbc.stride(1) == 1
-        assert dt_raw.shape == (T, heads) and dt_raw.stride(1) == 1 and state.shape[1:] == (heads, N, P)
+        assert state.shape[1:] == (heads, N, P)
+        assert fixed_decay is not None or (dt_raw.shape == (T, heads) and dt_raw.stride(1) == 1)
         y = torch.empty((T, heads * P), dtype=torch.float32, device=xbc.device)
         self.launches += 1
-        self.k.ssm_scan(_p(xbc), xbc.stride(0), _p(dt_raw), dt_raw.stride(0), _p(dt_bias), _p(A_log), _p(D), _p(state),
-                        _p(batch.cu_q), _p(batch.state_slot), _p(y), batch.num_requests, heads, P, N, groups,
-                        self._stream())
+        self.k.ssm_scan(_p(xbc), xbc.stride(0), _p(dt_raw), 0 if dt_raw is None else dt_raw.stride(0), _p(dt_bias),
+                        _p(A_log), _p(D), _p(state), _p(batch.cu_q), _p(batch.state_slot), _p(y), batch.num_requests,
+                        heads, P, N, groups, _p(fixed_decay), self._stream())
         return y
 
     def delta_scan(self, proj, offsets, lw, a_bias, state, batch, heads, d, unit_eps, decay_coef):
@@ -220,6 +222,64 @@ class NativeOps:
                           _p(state), _p(batch.cu_q), _p(batch.state_slot), _p(o), batch.num_requests, heads, d,
                           float(unit_eps), float(decay_coef), self._stream())
         return o
+
+    def selective_scan(self, x, dt_raw, bc, z, dt_bias, A_log, D, state, batch, out_dtype):
+        """Diagonal state-space scan with a step size per channel: ``x, dt_raw, z [T, inner]``, ``bc [T, 2 N]`` (B then
+        C), all 32-bit and possibly column slices; ``state [slots, inner, N]`` is read and left up to date.  Returns
+        ``y * silu(z)`` in ``out_dtype``."""
+        T, inner = x.shape
+        N = A_log.shape[1]
+        for t in (x, dt_raw, bc, z):
+            assert t.dtype == torch.float32 and t.stride(1) == 1 and t.shape[0] == T
+        assert dt_raw.shape[1] == inner and z.shape[1] == inner and bc.shape[1] == 2 * N
+        assert A_log.shape == (inner, N) and state.shape[1:] == (inner, N) and A_log.is_contiguous()
+        out = torch.empty((T, inner), dtype=out_dtype, device=x.device)
+        self.launches += 1
+        self.k.selective_scan(_p(x), x.stride(0), _p(dt_raw), dt_raw.stride(0), _p(bc), bc.stride(0), _p(z), z.stride(0),
+                              _p(dt_bias), _p(A_log), _p(D), _p(state), _p(batch.cu_q), _p(batch.state_slot), _p(out),
+                              inner, batch.num_requests, inner, N, _dt(out_dtype), self._stream())
+        return out
+
+    def qk_norm_write(self, qkv, positions, qn_w, kn_w, eps, temp_coef, temp_every, slots, k_cache, v_cache, nh, nkv, d,
+                      dv, D, out_dtype):
+        """Norms over the whole query and key projections, the query temperature, and the write of k and v at the
+        tokens' slots, every head ``D`` wide (zeros beyond its own size).  Returns q ``[T, nh * D]``."""
+        T = qkv.shape[0]
+        assert qkv.dtype == torch.float32 and qkv.stride(1) == 1 and qkv.shape[1] >= (nh + nkv) * d + nkv * dv
+        total_pages, nkv_c, page_size, D_c = k_cache.shape
+        assert (nkv_c, D_c) == (nkv, D) and k_cache.dtype == out_dtype and v_cache.shape == k_cache.shape
+        q = torch.empty((T, nh * D), dtype=out_dtype, device=qkv.device)
+        self.launches += 1
+        self.k.qk_norm_write(_p(qkv), qkv.stride(0), _p(positions), _p(qn_w), _p(kn_w), float(eps), float(temp_coef),
+                             int(temp_every), _p(slots), _p(q), _p(k_cache), _p(v_cache), T, nh, nkv, d, dv, D,
+                             page_size, total_pages, _dt(out_dtype), self._stream())
+        return q
+
+    def rotate_heads(self, x, positions, inv_freq, rot_dims, heads, dim, off_a, scale_a, off_b, scale_b):
+        """Rotary positions in place on two runs of heads of the 32-bit rows ``x`` (columns ``off_a`` and ``off_b``),
+        each run then multiplied by its factor."""
+        T = x.shape[0]
+        assert x.dtype == torch.float32 and x.stride(1) == 1
+        assert max(off_a, off_b) + heads * dim <= x.shape[1]
+        self.launches += 1
+        self.k.rotate_heads(_p(x), x.stride(0), _p(positions), _p(inv_freq), int(rot_dims), T, heads, dim, int(off_a),
+                            float(scale_a), int(off_b), float(scale_b), self._stream())
+
+    def branch_norm_add(self, resid, a, wa, b, wb, eps, coef):
+        """``resid += coef * (rms_norm(a) * wa + rms_norm(b) * wb)`` (``b`` None: one branch); all 32-bit ``[T, H]``."""
+        T, H = resid.shape
+        assert a.shape == (T, H) and a.is_contiguous() and resid.is_contiguous() and (b is None or b.shape == (T, H))
+        self.launches += 1
+        self.k.branch_norm_add(_p(resid), _p(a), _p(wa), _p(b), _p(wb), float(eps), float(coef), T, H, self._stream())
+
+    def concat_rows(self, a, b, out_dtype):
+        """``[a | b]`` in ``out_dtype`` (a, b 32-bit ``[T, H]``)."""
+        T, H = a.shape
+        assert a.dtype == torch.float32 and b.shape == (T, H) and a.is_contiguous() and b.is_contiguous()
+        out = torch.empty((T, 2 * H), dtype=out_dtype, device=a.device)
+        self.launches += 1
+        self.k.concat_rows(_p(a), _p(b), _p(out), T, H, _dt(out_dtype), self._stream())
+        return out
 
     # ------------------------------------------------------- latent attention
     def latent_prep(self, proj, off_q, q_rank, qn_w, off_kv, rank, kvn_w, dr, inv_freq, rot_dims, positions, slots,
@@ -317,6 +377,17 @@ class NativeOps:
         assert w.shape[1] == K and resid.shape == (M, N) and resid.dtype == torch.float32
         self._gemm(a, w, resid, M, N, K, self.k.EPI_ADD)
 
+    def linear_act(self, a, w, act):
+        """``act(a · w^T)`` in the activation dtype; ``act`` as in ``activation``.  The exact gelu is the product's
+        epilogue, the other activations a kernel behind a 32-bit product."""
+        (M, K), N = a.shape, w.shape[0]
+        assert w.shape[1] == K and a.dtype == w.dtype
+        if act == "gelu":
+            out = torch.empty((M, N), dtype=a.dtype, device=a.device)
+            self._gemm(a, w, out, M, N, K, self.k.EPI_GELU)
+            return out
+        return self.activation(self.linear(a, w, None, torch.float32), act, a.dtype)
+
     def linear_swiglu(self, a, w_gate_up):
         (M, K), N = a.shape, w_gate_up.shape[0]
         out = torch.empty((M, N // 2), dtype=a.dtype, device=a.device)
@@ -394,7 +465,8 @@ class NativeOps:
         return q
 
     def attention(self, q, k_cache, v_cache, block_table, cu_q, kv_len, window, scale, nh, nkv, hd, max_q_len,
-                  max_kv_len, num_single=0):
+                  max_kv_len, num_single=0, slopes=None):
+        """``slopes`` (32-bit ``[nh]`` or None): a score loses ``slopes[head] * (query position - key position)``."""
         T = q.shape[0]
         R, width = block_table.shape
         total_pages, _, page_size, _ = k_cache.shape
@@ -408,7 +480,7 @@ class NativeOps:
         decode_kernels = 1 if (q.dtype == torch.bfloat16 and hd in (16, 32, 48, 64, 96, 128)) else 2
         self.launches += 1 if scratch is None else (decode_kernels if num_single == R else decode_kernels + 1)
         self.k.attention(_p(q), _p(k_cache), _p(v_cache), _p(block_table), width, _p(cu_q), _p(kv_len), _p(out), T, R,
-                         nh, nkv, hd, page_size, total_pages, int(window), float(scale), int(max_q_len),
+                         nh, nkv, hd, page_size, total_pages, int(window), float(scale), _p(slopes), int(max_q_len),
                          int(max_kv_len), int(num_single), _p(scratch), _dt(q.dtype), self.fast, self._stream())
         return out
 
@@ -435,7 +507,7 @@ class NativeOps:
         return ids, wts, gate
 
     def route(self, h, w, E, k, norm, has_gate, norm_weight=None, eps=0.0, score="softmax", scale=1.0,
-              select_bias=None, input_settled=False):
+              select_bias=None, input_settled=False, logit_bias=None):
         """``router_topk`` and ``moe_permute`` together: ``(ids, wts, gate, offsets, rows, dest)``.  A step
         of at most 48 tokens does all of it in one launch.  ``input_settled``: ``h`` was not written by the
         kernel launched just before this call (it is a step's residual and a norm kernel ran in between); a
@@ -444,6 +516,10 @@ class NativeOps:
         assert w.shape == (E + (1 if has_gate else 0), H)
         assert h.dtype in (w.dtype, torch.float32) and (norm_weight is None or h.dtype == torch.float32)
         score_fn = {"softmax": 0, "sigmoid": 1}[score]
+        if logit_bias is not None:
+            # the router's own bias joins the logits before the softmax (and so the choice as well)
+            assert score == "softmax" and select_bias is None and logit_bias.shape == (E,)
+            score_fn, select_bias = 2, logit_bias
         h_is_f32 = int(norm_weight is None and h.dtype == torch.float32 and w.dtype != torch.float32)
         dev = h.device
         ids = torch.empty((T, k), dtype=torch.int32, device=dev)

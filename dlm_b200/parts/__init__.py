@@ -1,5 +1,5 @@
 """Built-in parts.  Importing this package registers them."""
-from . import attention, block, ffn, norm, recurrent, rope  # noqa: F401
+from . import attention, block, entry, ffn, norm, recurrent, rope  # noqa: F401
 from .base import (CacheTensor, FeedForward, GroupView, Mixer, Norm, PagedCache, PagedKV, PagedView, ParamSpec, Part, PartSpec,
                    PositionEncoding, RequestState, Runtime, StepBatch, StepContext)
 from .model import DecoderModel, LayerCall, ModelSpec, WeightError

@@ -173,5 +173,81 @@ def latent_attend(ops, q, gate, w_ukT, w_uv, sink, cache, block_table, batch, in
     return ops.latent_gate_out(val, gate, H, dv, cache.dtype)
 
 
+class NormedBiasedAttention(Mixer):
+    """Softmax attention without rotation whose positions enter through a distance penalty and a query temperature.
+
+    ``q, k, v = W h (+ bias)`` with ``heads`` query heads and ``kv_heads`` key/value heads (query head n reads
+    key/value head ``n // (heads / kv_heads)``), keys ``dim`` wide, values ``vdim`` wide.  With ``qk_norm`` the whole
+    query projection (all heads at once) is divided by its root mean square and multiplied by ``q.norm``; the key
+    projection likewise with ``k.norm``.  The query at position p is multiplied by
+    ``1 + temp_coef * ln(floor((p + 1) / temp_every) + 1)`` (``temp_every`` None: no temperature).  A score is
+    ``(q . k) * scale - slope_n * (p - j)`` with ``slope_n = 2^(-slope_bits (n + 1) / heads)`` (``slope_bits`` None:
+    no penalty); position p sees every ``j <= p`` (the last ``window`` of them when that is given); plain softmax;
+    ``W_o`` on the heads side by side.
+
+    Keys and values are cached with one head size ``max(dim, vdim)`` rounded up to a size the tensor-core kernels
+    take; entries beyond a head's own size are zeros, which change neither scores nor outputs, and ``W_o`` gets
+    zero columns for them at load."""
+
+    _HEAD_SIZES = (16, 32, 48, 64, 96, 128)
+
+    def __init__(self, hidden_size: int, heads: int, kv_heads: int, dim: int, vdim: int, scale: float, eps: float,
+                 qkv_bias: bool = True, qk_norm: bool = True, temp_coef: float = 0.0, temp_every: int | None = None,
+                 slope_bits: float | None = 8.0, window: int | None = None):
+        if heads % kv_heads:
+            raise ValueError("heads must be a multiple of kv_heads")
+        self.hidden, self.H, self.G, self.d, self.dv = int(hidden_size), int(heads), int(kv_heads), int(dim), int(vdim)
+        self.scale, self.eps = float(scale), float(eps)
+        self.qkv_bias, self.qk_norm = bool(qkv_bias), bool(qk_norm)
+        self.temp_coef = float(temp_coef)
+        self.temp_every = int(temp_every) if temp_every else 0
+        self.slope_bits = None if slope_bits is None else float(slope_bits)
+        self.window = int(window) if window else None
+        need = max(self.d, self.dv)
+        self.D = next((s for s in self._HEAD_SIZES if s >= need), -(-need // 8) * 8)
+        self.w_qkv = self.b_qkv = self.w_o = self.qn = self.kn = self.slopes = None
+
+    def param_specs(self):
+        H, G, d, dv = self.H, self.G, self.d, self.dv
+        specs = [ParamSpec("q", (H * d, self.hidden)), ParamSpec("k", (G * d, self.hidden)),
+                 ParamSpec("v", (G * dv, self.hidden)), ParamSpec("o", (self.hidden, H * dv))]
+        if self.qkv_bias:
+            specs += [ParamSpec("q.b", (H * d,), init="bias"), ParamSpec("k.b", (G * d,), init="bias"),
+                      ParamSpec("v.b", (G * dv,), init="bias")]
+        if self.qk_norm:
+            specs += [ParamSpec("q.norm", (H * d,), init="norm"), ParamSpec("k.norm", (G * d,), init="norm")]
+        return specs
+
+    def load(self, tensors, rt: Runtime):
+        self.w_qkv = torch.cat([rt.matrix(tensors[n]) for n in "qkv"], dim=0).contiguous()
+        self.b_qkv = torch.cat([rt.vector(tensors[n + ".b"]) for n in "qkv"]).contiguous() if self.qkv_bias else None
+        w_o = rt.matrix(tensors["o"])
+        if self.D != self.dv:       # zero columns where the stored heads are wider than the values
+            wide = torch.zeros((self.hidden, self.H, self.D), dtype=w_o.dtype, device=w_o.device)
+            wide[:, :, :self.dv] = w_o.reshape(self.hidden, self.H, self.dv)
+            w_o = wide.reshape(self.hidden, self.H * self.D).contiguous()
+        self.w_o = w_o
+        if self.qk_norm:
+            self.qn, self.kn = rt.vector(tensors["q.norm"]), rt.vector(tensors["k.norm"])
+        if self.slope_bits is not None:
+            self.slopes = torch.tensor([2.0 ** (-self.slope_bits * (n + 1) / self.H) for n in range(self.H)],
+                                       dtype=torch.float64).to(torch.float32).to(rt.device)
+
+    def cache_need(self):
+        return PagedKV(self.G, self.D, self.window)
+
+    def forward(self, h, resid, ctx: StepContext, call: int):
+        rt, ops, b = ctx.rt, ctx.rt.ops, ctx.batch
+        view = ctx.paged(call)
+        qkv = ops.linear(h, self.w_qkv, self.b_qkv, torch.float32)
+        q = ops.qk_norm_write(qkv, b.positions, self.qn, self.kn, self.eps, self.temp_coef, self.temp_every,
+                              view.group.slots if view.write else None, view.k, view.v, self.H, self.G, self.d, self.dv,
+                              self.D, rt.dtype)
+        o = ops.attention(q, view.k, view.v, view.group.block_table, b.cu_q, b.kv_len, self.window or 0, self.scale,
+                          self.H, self.G, self.D, b.max_q_len, b.max_kv_len, b.num_single, slopes=self.slopes)
+        ops.linear_add(o, self.w_o, resid)
+
+
 register_part("mixer", "gqa_attention", GroupedQueryAttention)
+register_part("mixer", "normed_biased_attention", NormedBiasedAttention)
 register_part("mixer", "latent_attention", LatentAttention)

@@ -45,6 +45,41 @@ class PreNormBlock(Part):
         self.ffn.forward(self.norm2.forward(resid, rt), resid, ctx, pre_norm=self.norm2)
 
 
+class ParallelBlock(PreNormBlock):
+    """``x += mixer(norm1(x)) + ffn(norm2(x))``: both sublayers read the same x, each through a norm of its own.
+    ``ffn`` None: the layer has no feed-forward (and no second norm).  The feed-forward runs first: its router may
+    read the residual itself (through ``norm2``), which must still be the layer's input then; the mixer's input was
+    normed before anything was added."""
+
+    def __init__(self, norm1: PartSpec, mixer: PartSpec, norm2: PartSpec | None = None, ffn: PartSpec | None = None,
+                 names: dict[str, str] | None = None):
+        self.norm1 = build_part("norm", norm1)
+        self.mixer = build_part("mixer", mixer)
+        self.ffn = build_part("ffn", ffn) if ffn is not None else None
+        self.norm2 = build_part("norm", norm2) if ffn is not None else None
+        self.names = {"norm1": "norm1.", "mixer": "mixer.", "norm2": "norm2.", "ffn": "ffn."}
+        if names:
+            self.names.update(names)
+
+    def children(self):
+        out = [(self.names["norm1"], self.norm1), (self.names["mixer"], self.mixer)]
+        if self.ffn is not None:
+            out += [(self.names["norm2"], self.norm2), (self.names["ffn"], self.ffn)]
+        return out
+
+    def load(self, tensors, rt):
+        for prefix, part in self.children():
+            mine = {prefix + s.name for s in part.param_specs()}
+            part.load({k[len(prefix):]: v for k, v in tensors.items() if k in mine}, rt)
+
+    def forward(self, resid, ctx: StepContext, call: int):
+        rt = ctx.rt
+        h1 = self.norm1.forward(resid, rt)
+        if self.ffn is not None:
+            self.ffn.forward(self.norm2.forward(resid, rt), resid, ctx, pre_norm=self.norm2)
+        self.mixer.forward(h1, resid, ctx, call)
+
+
 class HyperConnectionBlock(Part):
     """A pre-norm layer over S residual streams ``xs[:, s]`` instead of one.  For sublayer q (1: the mixer,
     2: the feed-forward) with learned ``in_q[S]``, ``mix_q[S, S]`` (indexed [from, to]) and ``out_q[S]``::
@@ -155,4 +190,5 @@ class HyperConnectionBlock(Part):
 
 
 register_part("block", "prenorm", PreNormBlock)
+register_part("block", "parallel", ParallelBlock)
 register_part("block", "hyper_connections", HyperConnectionBlock)

@@ -38,6 +38,29 @@ class DenseSwiGLU(FeedForward):
         ops.linear_add(act, self.w_down, resid)
 
 
+class DenseActMLP(FeedForward):
+    """``resid += down · act(up · h)`` without biases; ``activation``: "gelu_tanh" (the tanh form), "gelu" (the exact
+    form) or "silu".  The exact gelu sits in the first product's epilogue; the others are a kernel behind it."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "gelu_tanh"):
+        self.hidden, self.inter = int(hidden_size), int(intermediate_size)
+        if activation not in ("gelu_tanh", "gelu", "silu"):
+            raise ValueError(f"unknown activation {activation!r}")
+        self.act = activation
+        self.w_up = self.w_down = None
+
+    def param_specs(self):
+        return [ParamSpec("up", (self.inter, self.hidden)), ParamSpec("down", (self.hidden, self.inter))]
+
+    def load(self, tensors, rt: Runtime):
+        self.w_up, self.w_down = rt.matrix(tensors["up"]), rt.matrix(tensors["down"])
+
+    def forward(self, h, resid, ctx: StepContext, pre_norm=None):
+        ops = ctx.rt.ops
+        act = ops.linear_act(h, self.w_up, self.act)
+        ops.linear_add(act, self.w_down, resid)
+
+
 class SoftmaxTopKMoE(FeedForward):
     """Routed experts as the reference computes them (src/forward/cpu.rs:980-1048): router
     logits in 32-bit from the 32-bit normalised residual, softmax over all experts, the k largest probabilities (ties: lower
@@ -52,7 +75,19 @@ class SoftmaxTopKMoE(FeedForward):
 
     def __init__(self, hidden_size: int, num_experts: int, top_k: int, expert_intermediate_size: int,
                  norm_topk_prob: bool, shared_intermediate_size: int | None = None,
-                 shared_gate: bool | None = True):
+                 shared_gate: bool | None = True, router_bias: bool = False, names: dict[str, str] | None = None):
+        """``router_bias``: the router has a bias (tensor ``names["router_bias"]``) that is added to its logits; with
+        ``norm_topk_prob`` the weights are then the softmax over the chosen logits.  ``names``: the tensors' names
+        (``{e}`` stands for the expert's number), by default the ones of Qwen2-MoE checkpoints."""
+        self.names = {"router": "gate.weight", "router_bias": "gate.bias",
+                      "gate": "experts.{e}.gate_proj.weight", "up": "experts.{e}.up_proj.weight",
+                      "down": "experts.{e}.down_proj.weight", "shared_gate_proj": "shared_expert.gate_proj.weight",
+                      "shared_up": "shared_expert.up_proj.weight", "shared_down": "shared_expert.down_proj.weight",
+                      "shared_gate": "shared_expert_gate.weight"}
+        if names:
+            self.names.update(names)
+        self.router_bias = bool(router_bias)
+        self.b_router = None
         self.hidden, self.E, self.k, self.I = int(hidden_size), int(num_experts), int(top_k), int(expert_intermediate_size)
         if not (1 <= self.k <= self.E):
             raise ValueError("top_k must be in 1..num_experts")
@@ -63,42 +98,47 @@ class SoftmaxTopKMoE(FeedForward):
         self.w_router = self.w_gate_up = self.w_down = self.ws_gate_up = self.ws_down = None
 
     def param_specs(self):
-        specs = [ParamSpec("gate.weight", (self.E, self.hidden))]
+        nm = self.names
+        specs = [ParamSpec(nm["router"], (self.E, self.hidden))]
+        if self.router_bias:
+            specs.append(ParamSpec(nm["router_bias"], (self.E,), init="bias"))
         for e in range(self.E):
-            specs += [ParamSpec(f"experts.{e}.gate_proj.weight", (self.I, self.hidden)),
-                      ParamSpec(f"experts.{e}.up_proj.weight", (self.I, self.hidden)),
-                      ParamSpec(f"experts.{e}.down_proj.weight", (self.hidden, self.I))]
+            specs += [ParamSpec(nm["gate"].format(e=e), (self.I, self.hidden)),
+                      ParamSpec(nm["up"].format(e=e), (self.I, self.hidden)),
+                      ParamSpec(nm["down"].format(e=e), (self.hidden, self.I))]
         if self.Is:
-            specs += [ParamSpec("shared_expert.gate_proj.weight", (self.Is, self.hidden)),
-                      ParamSpec("shared_expert.up_proj.weight", (self.Is, self.hidden)),
-                      ParamSpec("shared_expert.down_proj.weight", (self.hidden, self.Is))]
+            specs += [ParamSpec(nm["shared_gate_proj"], (self.Is, self.hidden)),
+                      ParamSpec(nm["shared_up"], (self.Is, self.hidden)),
+                      ParamSpec(nm["shared_down"], (self.hidden, self.Is))]
             if self.shared_gate is not False:
-                specs.append(ParamSpec("shared_expert_gate.weight", (1, self.hidden),
-                                       optional=self.shared_gate is None))
+                specs.append(ParamSpec(nm["shared_gate"], (1, self.hidden), optional=self.shared_gate is None))
         return specs
 
     def load(self, tensors, rt: Runtime):
-        rows = [rt.matrix(tensors["gate.weight"])]
+        nm = self.names
+        rows = [rt.matrix(tensors[nm["router"]])]
+        self.b_router = rt.vector(tensors[nm["router_bias"]]) if self.router_bias else None
         self.has_gate = (self.shared_gate is True
-                         or (self.shared_gate is None and "shared_expert_gate.weight" in tensors))
+                         or (self.shared_gate is None and nm["shared_gate"] in tensors))
         if self.has_gate:
-            rows.append(rt.matrix(tensors["shared_expert_gate.weight"]).reshape(1, self.hidden))
+            rows.append(rt.matrix(tensors[nm["shared_gate"]]).reshape(1, self.hidden))
         self.w_router = torch.cat(rows, dim=0).contiguous()
         self.w_gate_up = torch.empty((self.E, 2 * self.I, self.hidden), dtype=rt.dtype, device=rt.device)
         self.w_down = torch.empty((self.E, self.hidden, self.I), dtype=rt.dtype, device=rt.device)
         for e in range(self.E):
-            self.w_gate_up[e, 0::2] = rt.matrix(tensors[f"experts.{e}.gate_proj.weight"])
-            self.w_gate_up[e, 1::2] = rt.matrix(tensors[f"experts.{e}.up_proj.weight"])
-            self.w_down[e] = rt.matrix(tensors[f"experts.{e}.down_proj.weight"])
+            self.w_gate_up[e, 0::2] = rt.matrix(tensors[nm["gate"].format(e=e)])
+            self.w_gate_up[e, 1::2] = rt.matrix(tensors[nm["up"].format(e=e)])
+            self.w_down[e] = rt.matrix(tensors[nm["down"].format(e=e)])
         if self.Is:
-            self.ws_gate_up = interleave_gate_up(rt.matrix(tensors["shared_expert.gate_proj.weight"]),
-                                                 rt.matrix(tensors["shared_expert.up_proj.weight"]))
-            self.ws_down = rt.matrix(tensors["shared_expert.down_proj.weight"])
+            self.ws_gate_up = interleave_gate_up(rt.matrix(tensors[nm["shared_gate_proj"]]),
+                                                 rt.matrix(tensors[nm["shared_up"]]))
+            self.ws_down = rt.matrix(tensors[nm["shared_down"]])
 
     def forward(self, h, resid, ctx: StepContext, pre_norm=None):
         ops = ctx.rt.ops
         rms = pre_norm.fusable_rms() if pre_norm is not None else None
         shared = None
+        bias = {"logit_bias": self.b_router} if self.b_router is not None else {}
         branch = ops.branch(h.shape[0])
         if self.Is:
             # the shared expert needs nothing from the router: it may run beside the routed experts
@@ -112,10 +152,11 @@ class SoftmaxTopKMoE(FeedForward):
             # one, the norm's or the shared expert's, only reads it)
             ids, wts, gate, offsets, rows, dest = ops.route(resid, self.w_router, self.E, self.k, self.norm,
                                                             self.has_gate, norm_weight=rms[0], eps=rms[1],
-                                                            input_settled=True)
+                                                            input_settled=True, **bias)
         else:
             x = h if pre_norm is None else pre_norm.forward(resid, ctx.rt, out_dtype=torch.float32)
-            ids, wts, gate, offsets, rows, dest = ops.route(x, self.w_router, self.E, self.k, self.norm, self.has_gate)
+            ids, wts, gate, offsets, rows, dest = ops.route(x, self.w_router, self.E, self.k, self.norm, self.has_gate,
+                                                            **bias)
         act = ops.grouped_swiglu(h, self.w_gate_up, offsets, rows)
         y = ops.grouped_linear(act, self.w_down, offsets)
         branch.join()
@@ -161,4 +202,5 @@ class TableRoutedExperts(FeedForward):
 
 register_part("ffn", "table_experts", TableRoutedExperts)
 register_part("ffn", "swiglu_dense", DenseSwiGLU)
+register_part("ffn", "dense_act", DenseActMLP)
 register_part("ffn", "moe_softmax_topk", SoftmaxTopKMoE)

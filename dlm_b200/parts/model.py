@@ -19,6 +19,8 @@ from .base import PagedView, ParamSpec, PartSpec, Runtime, StepBatch, StepContex
 class LayerCall:
     layer: int
     reads_cache_of: int | None = None   # index (in the order) of an earlier call whose cache is read
+    enters_pass: int | None = None      # t: this call opens pass t of a run of layers that is repeated; the model's
+                                        # ``pass_entry`` part makes the pass's input first
 
 
 @dataclass
@@ -37,6 +39,8 @@ class ModelSpec:
     embed_position_prefix: str = ""          # tensor-name prefix of that encoding's own tensors (if it has any)
     embed_scale: float = 1.0                 # the embedded tokens are multiplied by this
     residual_streams: int | None = None      # S: blocks get ``[T, S, hidden]`` (S equal copies at the start, summed at the end)
+    pass_entry: PartSpec | None = None       # what makes the input of a repeated run's pass (calls with ``enters_pass``)
+    pass_entry_prefix: str = ""              # tensor-name prefix of that part's tensors
 
 
 class WeightError(ValueError):
@@ -65,10 +69,13 @@ class DecoderModel:
         self.blocks = [build_part("block", bs) for bs in spec.layers]
         self.final_norm = build_part("norm", spec.final_norm)
         self.embed_position = build_part("position", spec.embed_position) if spec.embed_position else None
+        self.pass_entry = build_part("entry", spec.pass_entry) if spec.pass_entry else None
         self.order = list(spec.order) if spec.order is not None else [LayerCall(i) for i in range(len(self.blocks))]
         for ci, c in enumerate(self.order):
             if not (0 <= c.layer < len(self.blocks)):
                 raise ValueError(f"order names layer {c.layer}, the model has {len(self.blocks)}")
+            if c.enters_pass is not None and self.pass_entry is None:
+                raise ValueError(f"call {ci} opens a pass but the model has no pass_entry part")
             if c.reads_cache_of is not None:
                 if not (0 <= c.reads_cache_of < ci) or self.order[c.reads_cache_of].reads_cache_of is not None:
                     raise ValueError(f"call {ci} must read the cache of an earlier call that owns one")
@@ -86,6 +93,9 @@ class DecoderModel:
         if self.embed_position is not None:
             for p in self.embed_position.param_specs():
                 out[s.embed_position_prefix + p.name] = replace(p, name=s.embed_position_prefix + p.name)
+        if self.pass_entry is not None:
+            for p in self.pass_entry.param_specs():
+                out[s.pass_entry_prefix + p.name] = replace(p, name=s.pass_entry_prefix + p.name)
         for prefix, block in zip(s.layer_prefixes, self.blocks):
             for p in block.param_specs():
                 out[prefix + p.name] = replace(p, name=prefix + p.name)
@@ -124,6 +134,9 @@ class DecoderModel:
         if self.embed_position is not None:
             mine = {s.embed_position_prefix + p.name for p in self.embed_position.param_specs()}
             self.embed_position.load({n[len(s.embed_position_prefix):]: get(n) for n in names if n in mine}, rt)
+        if self.pass_entry is not None:
+            mine = {s.pass_entry_prefix + p.name for p in self.pass_entry.param_specs()}
+            self.pass_entry.load({n[len(s.pass_entry_prefix):]: get(n) for n in names if n in mine}, rt)
         for prefix, block in zip(s.layer_prefixes, self.blocks):
             block.load({n[len(prefix):]: get(n) for n in names if n.startswith(prefix)}, rt)
         self.final_norm.load({n[len(s.final_norm_prefix):]: get(n) for n in names
@@ -157,7 +170,11 @@ class DecoderModel:
             self.embed_position.on_embed(x, batch.positions, rt)
         if s.residual_streams is not None:
             x = ops.streams_expand(x, s.residual_streams)
+        # a model with repeated passes keeps the embedded tokens: blocks change x in place
+        x0 = x.clone() if self.pass_entry is not None else None
         for ci, c in enumerate(self.order):
+            if c.enters_pass is not None:
+                x = self.pass_entry.forward(x, x0, c.enters_pass, rt)
             self.blocks[c.layer].forward(x, ctx, ci)
         if s.residual_streams is not None:
             x = ops.streams_reduce(x, None, None, 0.0, torch.float32)

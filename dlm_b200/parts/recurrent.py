@@ -5,8 +5,11 @@ import math
 
 import torch
 
-from ..registry import register_part
-from .base import Mixer, ParamSpec, RequestState, Runtime, StepContext
+from dataclasses import replace
+
+from ..registry import build_part, register_part
+from .base import Mixer, ParamSpec, PartSpec, RequestState, Runtime, StepContext
+from .rope import rope_inv_freqs
 
 
 class Mamba2Mixer(Mixer):
@@ -117,5 +120,172 @@ class GeneralDeltaMixer(Mixer):
         ops.linear_add(g, self.w_o, resid)
 
 
+class Mamba1Mixer(Mixer):
+    """Selective state-space mixer with a decay per channel and state and a step size per channel.
+    ``W_in h = [x: inner | z: inner]``; x passes a causal convolution per channel (``conv_taps`` taps with bias, the
+    last tap meets the current token) and silu.  ``W_x x = [dt: dt_rank | B: state | C: state]``;
+    ``dt = softplus(W_dt dt + dt.b)`` per channel; ``A = -exp(A_log)`` (inner x state).  Per channel c and state n::
+
+        S[c, n] <- exp(dt_c A[c, n]) S[c, n] + dt_c x_c B_n          (S 32-bit, zero at a request's start)
+        y_c = sum_n S[c, n] C_n + D_c x_c
+
+    then ``y * silu(z)`` and ``W_o``.  A request's state: S and the convolution's last ``conv_taps - 1`` inputs.
+    Between the projections everything is 32-bit; the scan reads the 32-bit x, the projections its rounding."""
+
+    def __init__(self, hidden_size: int, inner: int, state: int, dt_rank: int, conv_taps: int):
+        self.hidden, self.inner, self.N, self.R = int(hidden_size), int(inner), int(state), int(dt_rank)
+        self.taps = int(conv_taps)
+        if self.taps < 1:
+            raise ValueError("the convolution has at least one tap")
+        self.w_in = self.w_x = self.w_dt = self.w_o = None
+        self.conv_w = self.conv_b = self.dt_b = self.A_log = self.D = None
+
+    def param_specs(self):
+        return [ParamSpec("in", (2 * self.inner, self.hidden)), ParamSpec("conv", (self.inner, self.taps)),
+                ParamSpec("conv.b", (self.inner,), init="bias"), ParamSpec("x", (self.R + 2 * self.N, self.inner)),
+                ParamSpec("dt", (self.inner, self.R)), ParamSpec("dt.b", (self.inner,), init="bias"),
+                ParamSpec("A_log", (self.inner, self.N), init="bias"), ParamSpec("D", (self.inner,), init="norm"),
+                ParamSpec("o", (self.hidden, self.inner))]
+
+    def load(self, tensors, rt: Runtime):
+        self.w_in, self.w_x, self.w_o = (rt.matrix(tensors[n]) for n in ("in", "x", "o"))
+        self.w_dt = rt.matrix(tensors["dt"])
+        self.conv_w, self.conv_b = rt.vector(tensors["conv"]), rt.vector(tensors["conv.b"])
+        self.dt_b, self.A_log, self.D = (rt.vector(tensors[n]) for n in ("dt.b", "A_log", "D"))
+
+    def state_need(self):
+        need = {"scan": RequestState((self.inner, self.N))}
+        if self.taps > 1:
+            need["conv"] = RequestState((self.taps - 1, self.inner))
+        return need
+
+    def forward(self, h, resid, ctx: StepContext, call: int):
+        rt, ops, b = ctx.rt, ctx.rt.ops, ctx.batch
+        xz = ops.linear(h, self.w_in, None, torch.float32)
+        conv_state = ctx.state(call, "conv") if self.taps > 1 else torch.empty((0, 0, self.inner), device=h.device)
+        x = ops.causal_conv(xz[:, :self.inner], self.conv_w, self.conv_b, conv_state, b, False, True, torch.float32)
+        low = ops.linear(x if rt.dtype == torch.float32 else ops.activation(x, "copy", rt.dtype), self.w_x, None,
+                         torch.float32)
+        dt_in = low[:, :self.R]
+        dt_in = dt_in.contiguous() if rt.dtype == torch.float32 else ops.activation(dt_in, "copy", rt.dtype)
+        dt_raw = ops.linear(dt_in, self.w_dt, None, torch.float32)
+        y = ops.selective_scan(x, dt_raw, low[:, self.R:], xz[:, self.inner:], self.dt_b, self.A_log, self.D,
+                               ctx.state(call, "scan"), b, rt.dtype)
+        ops.linear_add(y, self.w_o, resid)
+
+
+class RetentionMixer(Mixer):
+    """Linear attention with a constant decay per head, no softmax and no denominator.  ``q, k = W h`` (heads x
+    dim), ``v = W h`` (heads x vdim), no biases; rotary positions on the first ``rope_dims`` entries of every q and k
+    head (entry i with i + rope_dims / 2, angle ``position * rope_base^(-2i / rope_dims)``); k is multiplied by
+    ``dim^(-1/2)`` after the rotation.  Per head n::
+
+        S <- decay_n S + k v^T          (S: dim x vdim, 32-bit, zero at a request's start)
+        o = S^T q
+
+    Each head's o is divided by its root mean square (no weight), the heads side by side are multiplied by
+    ``silu(W_g h)``, then ``W_o``.  The scan is the state-space scan with constant decays and step size 1 (keys as
+    its B, queries as its C, one group per head)."""
+
+    def __init__(self, hidden_size: int, heads: int, dim: int, vdim: int, decay: list[float], eps: float,
+                 rope_base: float | None = None, rope_dims: int = 0):
+        self.hidden, self.H, self.d, self.dv, self.eps = int(hidden_size), int(heads), int(dim), int(vdim), float(eps)
+        self.decay = [float(v) for v in decay]
+        if len(self.decay) != self.H:
+            raise ValueError(f"{self.H} heads need {self.H} decays, got {len(self.decay)}")
+        self.rope_dims = int(rope_dims) if rope_base is not None else 0
+        self.rope_base = float(rope_base) if rope_base is not None else 0.0
+        if self.rope_dims % 2 or not (0 <= self.rope_dims <= self.d):
+            raise ValueError(f"rope_dims must be even and at most dim, got {self.rope_dims}")
+        self.w_in = self.w_o = self._freq = self._decay = None
+
+    def param_specs(self):
+        H, d, dv = self.H, self.d, self.dv
+        return [ParamSpec("q", (H * d, self.hidden)), ParamSpec("k", (H * d, self.hidden)),
+                ParamSpec("v", (H * dv, self.hidden)), ParamSpec("g", (H * dv, self.hidden)),
+                ParamSpec("o", (self.hidden, H * dv))]
+
+    def load(self, tensors, rt: Runtime):
+        # rows [v | k | q | g]: the scan reads values, keys and queries side by side in that order
+        self.w_in = torch.cat([rt.matrix(tensors[n]) for n in ("v", "k", "q", "g")], dim=0).contiguous()
+        self.w_o = rt.matrix(tensors["o"])
+        self._decay = torch.tensor(self.decay, dtype=torch.float64).to(torch.float32).to(rt.device)
+        self._freq = rope_inv_freqs(self.rope_dims, self.rope_base, self.rope_dims).to(rt.device) \
+            if self.rope_dims else None
+
+    def state_need(self):
+        return {"retention": RequestState((self.H, self.d, self.dv))}
+
+    def forward(self, h, resid, ctx: StepContext, call: int):
+        rt, ops, b = ctx.rt, ctx.rt.ops, ctx.batch
+        H, d, dv = self.H, self.d, self.dv
+        proj = ops.linear(h, self.w_in, None, torch.float32)               # [v | k | q | g]
+        ops.rotate_heads(proj, b.positions, self._freq, self.rope_dims, H, d, H * dv, d ** -0.5, H * dv + H * d, 1.0)
+        o = ops.ssm_scan(proj[:, :H * dv + 2 * H * d], None, None, None, None, ctx.state(call, "retention"), b, H, dv,
+                         d, H, fixed_decay=self._decay)
+        g = ops.gated_rmsnorm(o, proj[:, H * dv + 2 * H * d:], None, H, self.eps, "silu_after", rt.dtype)
+        ops.linear_add(g, self.w_o, resid)
+
+
+class ParallelMixers(Mixer):
+    """Two mixers side by side that read the same input.  Each output is RMS-normed over the model width with a
+    weight of its own (``<name>.out``); the result is ``coef`` times their sum (a half: the mean).  The children's
+    tensors lie under ``<name>.``; their caches and states are the pair's."""
+
+    def __init__(self, hidden_size: int, left: PartSpec, right: PartSpec, eps: float, coef: float = 0.5,
+                 names: tuple[str, str] = ("left", "right")):
+        self.hidden, self.eps, self.coef = int(hidden_size), float(eps), float(coef)
+        self.names = tuple(names)
+        self.parts = (build_part("mixer", left), build_part("mixer", right))
+        self.w_out = [None, None]
+        if sum(p.cache_need() is not None for p in self.parts) > 1:
+            raise ValueError("only one of two mixers side by side may keep paged keys and values")
+
+    @property
+    def graph_safe(self):
+        return all(p.graph_safe for p in self.parts)
+
+    def param_specs(self):
+        out = []
+        for name, part in zip(self.names, self.parts):
+            out += [replace(s, name=f"{name}.{s.name}") for s in part.param_specs()]
+            out.append(ParamSpec(f"{name}.out", (self.hidden,), init="norm"))
+        return out
+
+    def load(self, tensors, rt: Runtime):
+        for i, (name, part) in enumerate(zip(self.names, self.parts)):
+            mine = {f"{name}.{s.name}" for s in part.param_specs()}
+            part.load({k[len(name) + 1:]: v for k, v in tensors.items() if k in mine}, rt)
+            self.w_out[i] = rt.vector(tensors[f"{name}.out"])
+
+    def cache_need(self):
+        return next((p.cache_need() for p in self.parts if p.cache_need() is not None), None)
+
+    def state_need(self):
+        need = {}
+        for part in self.parts:
+            s = part.state_need()
+            if s is None:
+                continue
+            s = s if isinstance(s, dict) else {"": s}
+            clash = set(s) & set(need)
+            if clash:
+                raise ValueError(f"two mixers side by side both name a state {sorted(clash)}")
+            need.update(s)
+        return need or None
+
+    def forward(self, h, resid, ctx: StepContext, call: int):
+        ops = ctx.rt.ops
+        outs = []
+        for part in self.parts:
+            y = torch.zeros_like(resid)
+            part.forward(h, y, ctx, call)
+            outs.append(y)
+        ops.branch_norm_add(resid, outs[0], self.w_out[0], outs[1], self.w_out[1], self.eps, self.coef)
+
+
+register_part("mixer", "mamba1", Mamba1Mixer)
+register_part("mixer", "retention", RetentionMixer)
+register_part("mixer", "parallel_mixers", ParallelMixers)
 register_part("mixer", "mamba2", Mamba2Mixer)
 register_part("mixer", "general_delta", GeneralDeltaMixer)

@@ -12,7 +12,7 @@ from .config.base import ConfigError, read_config_json
 
 _ARCHITECTURES: dict[str, tuple[Any, Callable]] = {}
 _MODEL_TYPES: dict[str, str] = {}
-_PARTS: dict[str, dict[str, type]] = {"norm": {}, "position": {}, "mixer": {}, "ffn": {}, "block": {}}
+_PARTS: dict[str, dict[str, type]] = {"norm": {}, "position": {}, "mixer": {}, "ffn": {}, "block": {}, "entry": {}}
 
 
 def register_architecture(name: str, config_cls, build_spec: Callable, model_type: str | None = None) -> None:
@@ -87,4 +87,4 @@ def _ensure_builtin() -> None:
         return
     _builtin_done = True
     from . import parts  # noqa: F401  registers the built-in parts
-    from .models import qwen2_moe, zesapel  # noqa: F401  register the architectures
+    from .models import qwen2_moe, zasazen, zesapel  # noqa: F401  register the architectures

@@ -86,6 +86,10 @@ class PlainOps:
             v = torch.tanh(x)
         elif op == "gelu":
             v = 0.5 * x * (1.0 + torch.erf(x * 0.7071067811865476))
+        elif op == "gelu_tanh":
+            v = 0.5 * x * (1.0 + torch.tanh(0.7978845608028654 * (x + 0.044715 * x * x * x)))
+        elif op == "copy":
+            v = x
         else:
             v = x / (1.0 + torch.exp(-x))
         return v.to(out_dtype)
@@ -94,18 +98,28 @@ class PlainOps:
         T, C = y.shape
         v = y * (gate / (1.0 + torch.exp(-gate))) if mode == "silu_before" else y
         v = v.reshape(T, groups, C // groups)
-        v = (v * (1.0 / torch.sqrt((v * v).mean(-1, keepdim=True) + eps))).reshape(T, C) * w
+        v = (v * (1.0 / torch.sqrt((v * v).mean(-1, keepdim=True) + eps))).reshape(T, C)
+        if w is not None:
+            v = v * w
         if mode == "sigmoid_after":
             v = v * torch.sigmoid(gate)
+        elif mode == "silu_after":
+            v = v * (gate / (1.0 + torch.exp(-gate)))
         return v.to(out_dtype)
 
-    def ssm_scan(self, xbc, dt_raw, dt_bias, A_log, D, state, batch, heads, P, N, groups):
+    def ssm_scan(self, xbc, dt_raw, dt_bias, A_log, D, state, batch, heads, P, N, groups, fixed_decay=None):
         T = xbc.shape[0]
         inner = heads * P
         y = torch.zeros((T, inner), dtype=torch.float32, device=xbc.device)
         cu, slots = batch.cu_q.tolist(), batch.state_slot.tolist()
-        dt = torch.nn.functional.softplus(dt_raw + dt_bias, threshold=30.0)
-        decay = torch.exp(-torch.exp(A_log) * dt)                     # [T, heads]
+        if fixed_decay is not None:
+            dt = torch.ones((T, heads), dtype=torch.float32, device=xbc.device)
+            decay = fixed_decay[None, :].expand(T, heads)
+        else:
+            dt = torch.nn.functional.softplus(dt_raw + dt_bias, threshold=30.0)
+            decay = torch.exp(-torch.exp(A_log) * dt)                 # [T, heads]
+        if D is None:
+            D = torch.zeros(heads, dtype=torch.float32, device=xbc.device)
         per = heads // groups
         for r in range(batch.num_requests):
             S = state[slots[r]]                                        # [heads, N, P]
@@ -116,6 +130,60 @@ class PlainOps:
                 S.copy_(decay[t][:, None, None] * S + (dt[t][:, None] * B)[:, :, None] * x[:, None, :])
                 y[t] = (torch.einsum("hnp,hn->hp", S, C) + D[:, None] * x).reshape(inner)
         return y
+
+    def selective_scan(self, x, dt_raw, bc, z, dt_bias, A_log, D, state, batch, out_dtype):
+        T, inner = x.shape
+        N = A_log.shape[1]
+        out = torch.zeros((T, inner), dtype=torch.float32, device=x.device)
+        cu, slots = batch.cu_q.tolist(), batch.state_slot.tolist()
+        dt = torch.nn.functional.softplus(dt_raw + dt_bias, threshold=30.0)
+        A = -torch.exp(A_log)
+        for r in range(batch.num_requests):
+            S = state[slots[r]]                                        # [inner, N]
+            for t in range(cu[r], cu[r + 1]):
+                S.copy_(torch.exp(dt[t][:, None] * A) * S + (dt[t] * x[t])[:, None] * bc[t, :N][None, :])
+                out[t] = S @ bc[t, N:2 * N] + D * x[t]
+        return (out * (z / (1.0 + torch.exp(-z)))).to(out_dtype)
+
+    def qk_norm_write(self, qkv, positions, qn_w, kn_w, eps, temp_coef, temp_every, slots, k_cache, v_cache, nh, nkv, d,
+                      dv, D, out_dtype):
+        T = qkv.shape[0]
+        Q, K = nh * d, nkv * d
+        q, k, v = qkv[:, :Q], qkv[:, Q:Q + K], qkv[:, Q + K:Q + K + nkv * dv]
+        if qn_w is not None:
+            q = q / torch.sqrt((q * q).mean(-1, keepdim=True) + eps) * qn_w
+        if kn_w is not None:
+            k = k / torch.sqrt((k * k).mean(-1, keepdim=True) + eps) * kn_w
+        if temp_every > 0:
+            steps = torch.div(positions + 1, temp_every, rounding_mode="floor").to(torch.float32)
+            q = q * (1.0 + temp_coef * torch.log(steps + 1.0))[:, None]
+        pad = torch.nn.functional.pad
+        qo = pad(q.reshape(T, nh, d), (0, D - d)).reshape(T, nh * D)
+        if slots is not None:
+            ps = k_cache.shape[2]
+            sl = slots.long()
+            ok = sl >= 0
+            page, off = sl[ok] // ps, sl[ok] % ps
+            k_cache[page, :, off, :] = pad(k.reshape(T, nkv, d), (0, D - d))[ok].to(k_cache.dtype)
+            v_cache[page, :, off, :] = pad(v.reshape(T, nkv, dv), (0, D - dv))[ok].to(v_cache.dtype)
+        return qo.to(out_dtype)
+
+    def rotate_heads(self, x, positions, inv_freq, rot_dims, heads, dim, off_a, scale_a, off_b, scale_b):
+        T = x.shape[0]
+        for off, f in ((off_a, scale_a), (off_b, scale_b)):
+            v = x[:, off:off + heads * dim].reshape(T, heads, dim).clone()
+            if rot_dims:
+                v = self._rotate(v, positions, inv_freq, rot_dims)
+            x[:, off:off + heads * dim] = (v * f).reshape(T, heads * dim)
+
+    def branch_norm_add(self, resid, a, wa, b, wb, eps, coef):
+        v = a / torch.sqrt((a * a).mean(-1, keepdim=True) + eps) * wa
+        if b is not None:
+            v = v + b / torch.sqrt((b * b).mean(-1, keepdim=True) + eps) * wb
+        resid += coef * v
+
+    def concat_rows(self, a, b, out_dtype):
+        return torch.cat([a, b], dim=-1).to(out_dtype)
 
     def delta_scan(self, proj, offsets, lw, a_bias, state, batch, heads, d, unit_eps, decay_coef):
         T = proj.shape[0]
@@ -210,6 +278,9 @@ class PlainOps:
             out = out + bias
         return out.to(out_dtype)
 
+    def linear_act(self, a, w, act):
+        return self.activation(_f(a) @ _f(w).T, act, a.dtype)
+
     def linear_add(self, a, w, resid):
         resid += _f(a) @ _f(w).T
 
@@ -287,7 +358,7 @@ class PlainOps:
         return q.reshape(T, Q).to(out_dtype)
 
     def attention(self, q, k_cache, v_cache, block_table, cu_q, kv_len, window, scale, nh, nkv, hd, max_q_len,
-                  max_kv_len, num_single=0):
+                  max_kv_len, num_single=0, slopes=None):
         T = q.shape[0]
         ps = k_cache.shape[2]
         out = torch.zeros((T, nh * hd), dtype=torch.float32, device=q.device)
@@ -311,6 +382,8 @@ class PlainOps:
                 ok &= (qpos[:, None] - pos[None, :]) < window
             for h in range(nh):
                 s = (qs[:, h, :] @ k[:, h // group, :].T) * scale
+                if slopes is not None:
+                    s = s - slopes[h] * (qpos[:, None] - pos[None, :]).to(torch.float32)
                 s = s.masked_fill(~ok, float("-inf"))
                 p = torch.softmax(s, dim=-1)
                 out[cu[r]:cu[r + 1], h * hd:(h + 1) * hd] = p @ v[:, h // group, :]
@@ -318,7 +391,7 @@ class PlainOps:
 
     # ------------------------------------------------------------------- moe
     def router_topk(self, h, w, E, k, norm, has_gate, norm_weight=None, eps=0.0, score="softmax", scale=1.0,
-                    select_bias=None):
+                    select_bias=None, logit_bias=None):
         if norm_weight is not None:
             h = self.rmsnorm(h, norm_weight, eps, torch.float32)
         logits = _f(h) @ _f(w).T
@@ -326,6 +399,8 @@ class PlainOps:
         if has_gate:
             gate = 1.0 / (1.0 + torch.exp(-logits[:, E]))
             logits = logits[:, :E]
+        if logit_bias is not None:
+            logits = logits + logit_bias[None, :]
         probs = torch.softmax(logits, dim=-1) if score == "softmax" else 1.0 / (1.0 + torch.exp(-logits))
         pick = probs if select_bias is None else probs + select_bias[None, :].to(probs.dtype)
         ids = torch.sort(pick, dim=-1, descending=True, stable=True).indices[:, :k]
