@@ -11,9 +11,7 @@ the current layer; positions count from 0.
 """
 from __future__ import annotations
 
-import json
 import math
-import os
 
 import torch
 
@@ -206,6 +204,7 @@ class PlainZasazen:
         self.cfg, self.dtype, self.rounded = cfg, dtype, rounded
         self.t = tensors
         self._conv = {}
+        self.gaps = []
 
     def w(self, name):
         if name not in self._conv:
@@ -243,6 +242,8 @@ class PlainZasazen:
         if mlp is not None:
             h2 = rms_norm(x, self.w(f"l{i}.norm2"), eps)
             y = y + (dense_ff(h2, pf, r) if mlp["kind"] == "dense" else routed_ff(h2, pf, mlp, r))
+            if mlp["kind"] == "moe":
+                self.gaps.append(router_gap(h2, pf, mlp))
         return x + y
 
     def forward(self, tokens, return_layers=False):
@@ -251,6 +252,7 @@ class PlainZasazen:
         x0 = self.w("embed")[torch.tensor(tokens)] * cfg["embedding"]["scale"]
         x = x0
         seen = []
+        self.gaps = []          # per routed layer run: every position's gap between the last chosen and the next logit
         for i, enters in self.order():
             if enters is not None:
                 x = as_stored(torch.cat([x, x0], dim=-1), r) @ self.w("loop.in").T + self.w("loop.step")[enters]
@@ -259,3 +261,10 @@ class PlainZasazen:
         n = rms_norm(x, self.w("final.norm"), cfg["norm"]["eps"])
         logits = as_stored(n, r) @ self.w("head").T
         return (logits, torch.stack(seen)) if return_layers else logits
+
+    def smallest_gap(self, tokens):
+        """Per position, the smallest router gap over all routed layer runs (inf without routed layers)."""
+        self.forward(tokens)
+        if not self.gaps:
+            return torch.full((len(tokens),), float("inf"), dtype=self.dtype)
+        return torch.stack(self.gaps).min(0).values
