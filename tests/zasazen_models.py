@@ -187,13 +187,13 @@ def row_error(got, ref):
 # what a correct engine stays within (rounding of the format; measured values are printed by the tests)
 TOL = {"float32": 2e-4, "bfloat16": 6e-2}
 # router gaps (in logit units) below which rounding may choose another expert: such positions are not compared
-GAP = {"float32": 1e-3, "bfloat16": 8e-2}
+GAP = {"float32": 1e-3, "bfloat16": 0.15}
 
 
 def references(oracle, reqs, dtype):
     """Per request the exact logits, a limit for every position (TOL, or in bfloat16 three times the error that
     rounding alone causes there where that is more) and which positions are compared at all (those whose routing is
-    not a close call, here and in the rounded model)."""
+    not a close call, here and in the rounded model; in bfloat16 also not within three positions after one)."""
     import plain_zasazen as plain
     ref = {rid: oracle.forward(t) for rid, t in reqs.items()}
     gap = {rid: oracle.smallest_gap(t) for rid, t in reqs.items()}
@@ -204,6 +204,13 @@ def references(oracle, reqs, dtype):
             lim[rid] = torch.maximum(lim[rid], 3.0 * row_error(rounded.forward(t), ref[rid]))
             gap[rid] = torch.minimum(gap[rid], rounded.smallest_gap(t))
     clear = {rid: gap[rid] > GAP[dtype] for rid in reqs}
+    if dtype == "bfloat16":
+        # another expert at one position reaches the next few through the recurrences: those are left out as well
+        for rid, c in clear.items():
+            near = c.clone()
+            for back in (1, 2, 3):
+                near[back:] &= c[:-back]
+            clear[rid] = near
     return ref, lim, clear
 
 
