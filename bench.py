@@ -10,6 +10,7 @@ continuous-batching workload on the windowed variant of the model (`serving`).
     python bench.py --workload sweep        # decode at 1k-32k tokens of context, prompts of 8k and 16k
     python bench.py --workload kernels      # the weight-streaming product alone, by shape and row length
     python bench.py --workload zesapel      # the Zesapel design beside Qwen2-MoE at equal sizes, and its kernels alone
+    python bench.py --workload zasazen      # the Zasazen design beside Qwen2-MoE at equal sizes, and its kernels alone
 
 A step is one decode step of the whole batch.  One JSON line is printed.
 """
@@ -714,6 +715,178 @@ def run_zesapel(args, pk) -> dict:
     return out
 
 
+# ------------------------------------------------------------------ the Zasazen design beside Qwen2-MoE
+def zasazen_config(width, vocab=32768):
+    """Layer sizes that resemble a real model's: 64-wide attention heads with four query heads a key/value head,
+    retention heads of 64 x 128, a selective scan twice as wide as the model with 16 states a channel, a gelu
+    feed-forward four times the width, 16 gated experts of half the width with a shared one of the width; the two
+    middle layers run twice (8 layer runs)."""
+    moe = {"kind": "moe", "router": {"experts": 16, "top": 2}, "expert": {"ff": width // 2}, "shared": {"ff": width}}
+    dense = {"kind": "dense", "ff": 4 * width}
+    hr = width // 128
+    pair = {"type": "parallel", "mixer": {
+        "left": {"heads": width // 64, "kv_heads": width // 256, "dim": 64, "vdim": 64, "scale": 0.125,
+                 "q_temp": {"coef": 0.5, "every": 512}},
+        "right": {"heads": hr, "dim": 64, "vdim": 128, "decay": [1.0 - 2.0 ** (-5 - 5 * i / max(hr - 1, 1)) for i in range(hr)],
+                  "rot": {"base": 1e6, "dims": 64}}}}
+    scan = {"type": "mamba1", "mixer": {"inner": 2 * width, "state": 16, "dt_rank": width // 16, "conv": 4}}
+    layers = [dict(pair, mlp=dense), dict(pair, mlp=moe), dict(scan, mlp=moe), dict(pair, mlp=dense), dict(scan, mlp=dense),
+              dict(pair, mlp=moe)]
+    return {"architecture": "Zasazen", "vocab": vocab, "width": width, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5},
+            "loop": {"start": 1, "stop": 3, "times": 2}, "layers": layers}
+
+
+def qwen_config_like_zasazen(z):
+    """Qwen2-MoE with the same width, vocabulary and as many layers as the design has layer runs; attention heads of
+    the same number and size; routed layers where the design's runs have experts (same experts, same shared one),
+    dense SwiGLU layers with as many weights as the gelu feed-forward (3 I' = 2 ff) elsewhere."""
+    from dlm_b200.models.zasazen import layer_order
+    width = z["width"]
+    runs = [z["layers"][c.layer] for c in layer_order(len(z["layers"]), z.get("loop"))]
+    left = z["layers"][0]["mixer"]["left"]
+    moe = next(L["mlp"] for L in z["layers"] if L["mlp"]["kind"] == "moe")
+    dense = next(L["mlp"] for L in z["layers"] if L["mlp"]["kind"] == "dense")
+    return dict(architectures=["Qwen2MoeForCausalLM"], model_type="qwen2_moe", num_hidden_layers=len(runs), hidden_size=width,
+                num_attention_heads=left["heads"], num_key_value_heads=left["kv_heads"], head_dim=left["dim"],
+                num_experts=moe["router"]["experts"], num_experts_per_tok=moe["router"]["top"],
+                moe_intermediate_size=moe["expert"]["ff"], shared_expert_intermediate_size=moe["shared"]["ff"],
+                norm_topk_prob=True, decoder_sparse_step=1,
+                mlp_only_layers=[i for i, L in enumerate(runs) if L["mlp"]["kind"] == "dense"],
+                intermediate_size=(2 * dense["ff"] // 3) // 64 * 64, vocab_size=z["vocab"], rope_theta=10000.0,
+                rms_norm_eps=1e-5, use_sliding_window=False, tie_word_embeddings=False, max_position_embeddings=8192)
+
+
+def zasazen_kernels(z, pk, batch, context, prefill_tokens):
+    """Each kernel of the design alone at the layer sizes of `z`: a prompt of `prefill_tokens` tokens of one request,
+    and a decode step of `batch` requests at `context` tokens.  Microseconds (median of 5, the cache flushed before
+    each), the bytes the kernel has to move at least, and that over time over the measured copy bandwidth; the
+    attention also without its distance penalty (the closest model's kernel at the same sizes) and with its flops."""
+    from types import SimpleNamespace
+
+    import torch
+
+    from dlm_b200.ops import native_ops
+    ops = native_ops(fast=True)
+    dev = "cuda"
+    W = z["width"]
+    pair = next(L["mixer"] for L in z["layers"] if L["type"] == "parallel")
+    ms = next(L["mixer"] for L in z["layers"] if L["type"] == "mamba1")
+    lf, rt = pair["left"], pair["right"]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    i32 = dict(dtype=torch.int32, device=dev)
+    rows = {}
+
+    def timed(name, case, fn, nbytes, flop=None):
+        ts = []
+        for _ in range(6):
+            _flush(torch, flush)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        us = statistics.median(ts[1:]) * 1e3
+        row = {"us": round(us, 1), "mbytes": round(nbytes / 1e6, 2),
+               "frac_of_copy": round(nbytes / (us * 1e-6) / 1e9 / pk["hbm_gbs"], 3)}
+        if flop is not None:
+            row["gflop"] = round(flop / 1e9, 2)
+            row["frac_of_bf16_peak"] = round(flop / (us * 1e-6) / (pk["bf16_tflops"] * 1e12), 4)
+        rows.setdefault(name, {})[case] = row
+
+    for case, lens, start in (("prefill", [prefill_tokens], 0), ("decode", [1] * batch, context)):
+        T, R = sum(lens), len(lens)
+        cu = [0]
+        for n in lens:
+            cu.append(cu[-1] + n)
+        b = SimpleNamespace(num_requests=R, cu_q=torch.tensor(cu, **i32), state_slot=torch.arange(R, **i32),
+                            token_req=torch.tensor([r for r, n in enumerate(lens) for _ in range(n)], **i32),
+                            positions=torch.tensor([start + i for n in lens for i in range(n)], **i32))
+        # selective scan and its convolution
+        inner, N, taps = ms["inner"], ms["state"], ms["conv"]
+        xz = torch.randn(T, 2 * inner, device=dev)
+        cw, cb = torch.randn(inner, taps, device=dev), torch.randn(inner, device=dev)
+        cst = torch.zeros(R + 1, taps - 1, inner, device=dev)
+        timed("causal_conv + silu (scan input)", case,
+              lambda: ops.causal_conv(xz[:, :inner], cw, cb, cst, b, False, True, torch.float32),
+              T * inner * 8 + 2 * R * (taps - 1) * inner * 4)
+        x, dt, bc = torch.randn(T, inner, device=dev), torch.randn(T, inner, device=dev), torch.randn(T, 2 * N, device=dev)
+        A_log, vec = torch.rand(inner, N, device=dev), torch.randn(inner, device=dev) * 0.1
+        sst = torch.zeros(R + 1, inner, N, device=dev)
+        timed("selective_scan", case, lambda: ops.selective_scan(x, dt, bc, xz[:, inner:], vec, A_log, vec, sst, b, torch.bfloat16),
+              T * (inner * 14 + 2 * N * 4) + 2 * R * inner * N * 4 + inner * N * 4)
+        # retention: rotation, scan with constant decays, head norm and gate
+        H2, d2, dv2 = rt["heads"], rt["dim"], rt["vdim"]
+        proj = torch.randn(T, 2 * H2 * dv2 + 2 * H2 * d2, device=dev)
+        freq = torch.tensor([1e6 ** (-2.0 * i / d2) for i in range(d2 // 2)], device=dev)
+        decay = torch.tensor(rt["decay"], device=dev)
+        rst = torch.zeros(R + 1, H2, d2, dv2, device=dev)
+        timed("rotate_heads (q, k in place)", case,
+              lambda: ops.rotate_heads(proj, b.positions, freq, d2, H2, d2, H2 * dv2, d2 ** -0.5, H2 * dv2 + H2 * d2, 1.0),
+              T * 2 * H2 * d2 * 8)
+        timed("ssm_scan with constant decays (retention)", case,
+              lambda: ops.ssm_scan(proj[:, :H2 * dv2 + 2 * H2 * d2], None, None, None, None, rst, b, H2, dv2, d2, H2,
+                                   fixed_decay=decay),
+              T * (H2 * dv2 * 2 + 2 * H2 * d2) * 4 + 2 * R * H2 * d2 * dv2 * 4)
+        o_ = torch.randn(T, H2 * dv2, device=dev)
+        timed("gated_rmsnorm (per head, silu gate)", case,
+              lambda: ops.gated_rmsnorm(o_, proj[:, H2 * dv2 + 2 * H2 * d2:], None, H2, 1e-5, "silu_after", torch.bfloat16),
+              T * H2 * dv2 * 10)
+        # attention: norms, temperature and cache write; then the attention with and without the distance penalty
+        H, G, d, dv = lf["heads"], lf["kv_heads"], lf["dim"], lf["vdim"]
+        D = max(d, dv)
+        held = start + max(lens)
+        pages_each = -(-held // 64)
+        k_cache = (torch.randn(R * pages_each + 1, G, 64, D, device=dev) * 0.3).to(torch.bfloat16)
+        v_cache = (torch.randn(R * pages_each + 1, G, 64, D, device=dev) * 0.3).to(torch.bfloat16)
+        table = torch.arange(R * pages_each, **i32).reshape(R, pages_each)
+        slots = torch.cat([table[r, (start + torch.arange(n, device=dev)) // 64] * 64 + (start + torch.arange(n, device=dev)) % 64
+                           for r, n in enumerate(lens)]).to(torch.int32)
+        qkv = torch.randn(T, (H + G) * d + G * dv, device=dev)
+        qn, kn = torch.randn(H * d, device=dev), torch.randn(G * d, device=dev)
+        timed("qk_norm_write", case,
+              lambda: ops.qk_norm_write(qkv, b.positions, qn, kn, 1e-5, 0.5, 512, slots, k_cache, v_cache, H, G, d, dv, D,
+                                        torch.bfloat16), T * ((H + G) * d + G * dv) * 4 + T * (H + 2 * G) * D * 2)
+        q = ops.qk_norm_write(qkv, b.positions, qn, kn, 1e-5, 0.5, 512, slots, k_cache, v_cache, H, G, d, dv, D, torch.bfloat16)
+        kv_len = torch.tensor([start + n for n in lens], **i32)
+        slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / H) for h in range(H)], device=dev)
+        single = sum(1 for n in lens if n == 1)
+        keys = sum(start + i + 1 for n in lens for i in range(n))
+        att_bytes = R * held * G * D * 4 + T * H * D * 4 if case == "decode" else held * G * D * 4 + T * H * D * 4
+        for name, sl in (("attention with distance penalty", slopes), ("attention without it (Qwen2-MoE's)", None)):
+            timed(name, case, lambda: ops.attention(q, k_cache, v_cache, table, b.cu_q, kv_len, 0, 0.125, H, G, D, max(lens),
+                                                    held, single, slopes=sl), att_bytes, flop=4.0 * keys * H * D)
+        # the pair's sum and the pass entry
+        ya, yb, resid = torch.randn(T, W, device=dev), torch.randn(T, W, device=dev), torch.randn(T, W, device=dev)
+        wv = torch.randn(W, device=dev)
+        timed("branch_norm_add", case, lambda: ops.branch_norm_add(resid, ya, wv, yb, wv, 1e-5, 0.5), T * W * 16)
+        timed("concat_rows (pass entry)", case, lambda: ops.concat_rows(ya, yb, torch.bfloat16), T * W * 12)
+        up = torch.randn(T, 4 * W, device=dev)
+        timed("activation gelu (tanh form)", case, lambda: ops.activation(up, "gelu_tanh", torch.bfloat16), T * 4 * W * 6)
+    ops.check_errors()
+    return rows
+
+
+def run_zasazen(args, pk) -> dict:
+    sampler = ClockSampler()
+    sampler.start()
+    t0 = time.time()
+    out = {"workload": "zasazen", "dtype": "bf16", "data": "synthetic: seeded uniform token ids, random weights N(0, 0.02)",
+           "peaks": pk, "sizes": {}, "l2": "a buffer larger than L2 is written before every timed step"}
+    for width in (1024, 2048):
+        z = zasazen_config(width)
+        q = qwen_config_like_zasazen(z)
+        out["sizes"][str(width)] = {
+            "layer_runs": q["num_hidden_layers"], "zasazen": measure_engine(z, args.batch, args.prompt_len, args.steps, 2048),
+            "qwen2_moe": measure_engine(q, args.batch, args.prompt_len, args.steps, 2048)}
+    out["kernels_width_2048"] = zasazen_kernels(zasazen_config(2048), pk, args.batch, args.prompt_len, 2048)
+    t1 = time.time()
+    time.sleep(0.2)
+    sampler.stop()
+    out["clocks"] = sampler.summary(t0, t1)
+    return out
+
+
 def layers_that_fit(raw, want, reserve_gb=40.0):
     """As many layers of `raw` (at most `want`) as the free device memory holds beside `reserve_gb` for
     the cache pool, the head, graphs and activations."""
@@ -773,7 +946,7 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 and prefill measurements")
     ap.add_argument("--no-extras", action="store_true", help="skip `sizes_57b` and `serving`")
     ap.add_argument("--only-prefill", action="store_true", help="measure the 2,048-token prefill alone (for profiles)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "sweep", "kernels", "zesapel"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "sweep", "kernels", "zesapel", "zasazen"],
                     help="serving: the continuous-batching workload on the windowed model, instead of the default line; "
                          "sweep: decode at contexts of 1k to 32k and prefill of longer prompts, a line of its own; "
                          "kernels: the weight-streaming product alone")
@@ -806,6 +979,9 @@ def main() -> int:
         return 0
     if args.workload == "zesapel":
         print(json.dumps(run_zesapel(args, pk)))
+        return 0
+    if args.workload == "zasazen":
+        print(json.dumps(run_zasazen(args, pk)))
         return 0
     max_batch = 64 if not args.no_points else args.batch
     m = Measurement(MODEL, args.layers, args.prompt_len, args.context, max_batch, pk, page=args.page_size)

@@ -13,7 +13,8 @@ enum Epilogue : int {
     EPI_STORE = 0,    // out[m, n] = acc (+ bias[n]), stored as the output dtype
     EPI_ADD = 1,      // out[m, n] += acc, out is float32 (the residual stream)
     EPI_SWIGLU = 2,   // out[m, n/2] = silu(acc[m, n]) * acc[m, n+1] for even n (interleaved weight rows)
-    EPI_GELU = 3      // out[m, n] = gelu(acc (+ bias[n])) in its exact (erf) form, stored as the output dtype
+    EPI_GELU = 3,     // out[m, n] = gelu(acc (+ bias[n])) in its exact (erf) form, stored as the output dtype
+    EPI_GELU_TANH = 4 // the same with gelu in its tanh form: z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))) / 2
 };
 
 // out[T, H] (f32) = table[tokens[t], :] * scale
@@ -216,6 +217,10 @@ void rotate_heads(float* x, int ld, const int32_t* positions, const float* inv_f
 // resid[t, :] += coef * (a[t] / rms(a[t]) * wa + b[t] / rms(b[t]) * wb)   (all f32 [T, H]; b == nullptr: one branch)
 void branch_norm_add(float* resid, const float* a, const float* wa, const float* b, const float* wb, float eps,
                      float coef, int T, int H, cudaStream_t stream);
+
+// out_a[t] = x[t] / rms(x[t]) * wa, out_b[t] = x[t] / rms(x[t]) * wb  (x, wa, wb f32; outputs in out_dtype)
+void rmsnorm_pair(const float* x, const float* wa, const float* wb, void* out_a, void* out_b, int T, int H, float eps,
+                  int out_dtype, cudaStream_t stream);
 
 // out[t, :] = [a[t, :] | b[t, :]] in out_dtype (a, b f32 [T, H])
 void concat_rows(const float* a, const float* b, void* out, int T, int H, int out_dtype, cudaStream_t stream);

@@ -18,6 +18,7 @@ PYBIND11_MODULE(_dlm_kernels, m) {
     m.attr("EPI_ADD") = (int)dlmk::EPI_ADD;
     m.attr("EPI_SWIGLU") = (int)dlmk::EPI_SWIGLU;
     m.attr("EPI_GELU") = (int)dlmk::EPI_GELU;
+    m.attr("EPI_GELU_TANH") = (int)dlmk::EPI_GELU_TANH;
 
     m.def("embed", [](u64 tokens, u64 table, u64 out, int T, int H, int V, float scale, int dtype, u64 stream) {
         dlmk::embed(ptr<const int32_t>(tokens), ptr<const void>(table), ptr<float>(out), T, H, V, scale, dtype,
@@ -174,6 +175,10 @@ PYBIND11_MODULE(_dlm_kernels, m) {
                                 u64 stream) {
         dlmk::branch_norm_add(ptr<float>(resid), ptr<const float>(a), ptr<const float>(wa), ptr<const float>(b),
                               ptr<const float>(wb), eps, coef, T, H, st(stream));
+    });
+    m.def("rmsnorm_pair", [](u64 x, u64 wa, u64 wb, u64 out_a, u64 out_b, int T, int H, float eps, int out_dtype, u64 stream) {
+        dlmk::rmsnorm_pair(ptr<const float>(x), ptr<const float>(wa), ptr<const float>(wb), ptr<void>(out_a),
+                           ptr<void>(out_b), T, H, eps, out_dtype, st(stream));
     });
     m.def("concat_rows", [](u64 a, u64 b, u64 out, int T, int H, int out_dtype, u64 stream) {
         dlmk::concat_rows(ptr<const float>(a), ptr<const float>(b), ptr<void>(out), T, H, out_dtype, st(stream));

@@ -102,8 +102,10 @@ __device__ __forceinline__ float gelu_exact_f(float z) { return 0.5f * z * (1.0f
 __device__ __forceinline__ float gelu_tanh_f(float z) {
     return 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
 }
-// What a storing epilogue does to acc (+ bias) before it rounds: gelu for EPI (an Epilogue of api.h) == 3, EPI_GELU;
-// nothing otherwise.
-template <int EPI> __device__ __forceinline__ float epi_act(float v) { return EPI == 3 ? gelu_exact_f(v) : v; }
+// What a storing epilogue does to acc (+ bias) before it rounds: gelu for EPI (an Epilogue of api.h) == 3, EPI_GELU,
+// its tanh form for 4, EPI_GELU_TANH; nothing otherwise.
+template <int EPI> __device__ __forceinline__ float epi_act(float v) {
+    return EPI == 3 ? gelu_exact_f(v) : (EPI == 4 ? gelu_tanh_f(v) : v);
+}
 
 }  // namespace dlmk

@@ -194,6 +194,7 @@ void launch_bm(const MmaParams& p, int epilogue, dim3 grid, cudaStream_t stream)
         case EPI_STORE: DLM_MMA(EPI_STORE, TOut) break;
         case EPI_ADD: DLM_MMA(EPI_ADD, float) break;
         case EPI_GELU: DLM_MMA(EPI_GELU, TOut) break;
+        case EPI_GELU_TANH: DLM_MMA(EPI_GELU_TANH, TOut) break;
         default: DLM_MMA(EPI_SWIGLU, TOut) break;
     }
 #undef DLM_MMA
@@ -207,7 +208,7 @@ void gemm_mma(const void* a, int lda, const int32_t* a_rows, const void* w, int 
     if (M <= 0 || N <= 0) return;
     DLM_CHECK(epilogue != EPI_SWIGLU || N % 2 == 0, "gemm: the SwiGLU epilogue needs an even N");
     DLM_CHECK(epilogue != EPI_ADD || out_dtype == F32, "gemm: the accumulate epilogue needs a float32 output");
-    DLM_CHECK(bias == nullptr || epilogue == EPI_STORE || epilogue == EPI_GELU, "gemm: a bias goes with a storing epilogue only");
+    DLM_CHECK(bias == nullptr || epilogue == EPI_STORE || epilogue == EPI_GELU || epilogue == EPI_GELU_TANH, "gemm: a bias goes with a storing epilogue only");
     MmaParams p{static_cast<const __nv_bfloat16*>(a), lda, a_rows, static_cast<const __nv_bfloat16*>(w), ldw,
                 w_expert_stride, expert_offsets, num_experts, bias, out, ldo, M, N, K};
     // grouped products have ragged groups: smaller row tiles waste less

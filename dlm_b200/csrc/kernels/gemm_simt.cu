@@ -136,6 +136,7 @@ void launch(const GemmParams& p, int epilogue, dim3 grid, cudaStream_t stream) {
         case EPI_ADD: gemm_simt_kernel<TIn, float, EPI_ADD><<<grid, THREADS, 0, stream>>>(p); break;
         case EPI_SWIGLU: gemm_simt_kernel<TIn, TOut, EPI_SWIGLU><<<grid, THREADS, 0, stream>>>(p); break;
         case EPI_GELU: gemm_simt_kernel<TIn, TOut, EPI_GELU><<<grid, THREADS, 0, stream>>>(p); break;
+        case EPI_GELU_TANH: gemm_simt_kernel<TIn, TOut, EPI_GELU_TANH><<<grid, THREADS, 0, stream>>>(p); break;
         default: DLM_CHECK(false, "gemm: unknown epilogue");
     }
 }
@@ -149,7 +150,7 @@ void gemm_simt(const void* a, int lda, const int32_t* a_rows, const void* w, int
     DLM_CHECK(K > 0, "gemm: K must be > 0");
     DLM_CHECK(epilogue != EPI_SWIGLU || N % 2 == 0, "gemm: the SwiGLU epilogue needs an even N");
     DLM_CHECK(epilogue != EPI_ADD || out_dtype == F32, "gemm: the accumulate epilogue needs a float32 output");
-    DLM_CHECK(bias == nullptr || epilogue == EPI_STORE || epilogue == EPI_GELU, "gemm: a bias goes with a storing epilogue only");
+    DLM_CHECK(bias == nullptr || epilogue == EPI_STORE || epilogue == EPI_GELU || epilogue == EPI_GELU_TANH, "gemm: a bias goes with a storing epilogue only");
     GemmParams p{a, lda, a_rows, w, ldw, w_expert_stride, expert_offsets, num_experts, bias, out, ldo, M, N, K};
     int m_tiles = (M + BM - 1) / BM;
     if (expert_offsets != nullptr) {

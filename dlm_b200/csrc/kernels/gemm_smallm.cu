@@ -208,6 +208,7 @@ void launch_nt(const SmallParams& p, int epilogue, dim3 grid, cudaStream_t strea
         case EPI_STORE: launch_dep(gemm_smallm_kernel<NT, EPI_STORE, TOut>, grid, WARPS * 32, 0, stream, p); break;
         case EPI_ADD: launch_dep(gemm_smallm_kernel<NT, EPI_ADD, float>, grid, WARPS * 32, 0, stream, p); break;
         case EPI_GELU: launch_dep(gemm_smallm_kernel<NT, EPI_GELU, TOut>, grid, WARPS * 32, 0, stream, p); break;
+        case EPI_GELU_TANH: launch_dep(gemm_smallm_kernel<NT, EPI_GELU_TANH, TOut>, grid, WARPS * 32, 0, stream, p); break;
         default: launch_dep(gemm_smallm_kernel<NT, EPI_SWIGLU, TOut>, grid, WARPS * 32, 0, stream, p); break;
     }
 }

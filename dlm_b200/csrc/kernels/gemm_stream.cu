@@ -399,6 +399,8 @@ void launch_nt(const StreamParams& p, int grid, int out_dtype, int epilogue, cud
         case EPI_ADD: launch_one<NT, NCH, EPI_ADD, float>(p, grid, stream); break;
         case EPI_GELU: if (f32) launch_one<NT, NCH, EPI_GELU, float>(p, grid, stream);
                        else launch_one<NT, NCH, EPI_GELU, __nv_bfloat16>(p, grid, stream); break;
+        case EPI_GELU_TANH: if (f32) launch_one<NT, NCH, EPI_GELU_TANH, float>(p, grid, stream);
+                       else launch_one<NT, NCH, EPI_GELU_TANH, __nv_bfloat16>(p, grid, stream); break;
         default: if (f32) launch_one<NT, NCH, EPI_SWIGLU, float>(p, grid, stream);
                  else launch_one<NT, NCH, EPI_SWIGLU, __nv_bfloat16>(p, grid, stream); break;
     }

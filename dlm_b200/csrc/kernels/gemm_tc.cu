@@ -252,7 +252,7 @@ bool gemm_tc(const void* a, int lda, const void* w, int ldw, const int32_t* expe
     if (M <= 0 || N <= 0) return true;
     DLM_CHECK(epilogue != EPI_SWIGLU || N % 2 == 0, "gemm: the SwiGLU epilogue needs an even N");
     DLM_CHECK(epilogue != EPI_ADD || out_dtype == F32, "gemm: the accumulate epilogue needs a float32 output");
-    DLM_CHECK(bias == nullptr || epilogue == EPI_STORE || epilogue == EPI_GELU, "gemm: a bias goes with a storing epilogue only");
+    DLM_CHECK(bias == nullptr || epilogue == EPI_STORE || epilogue == EPI_GELU || epilogue == EPI_GELU_TANH, "gemm: a bias goes with a storing epilogue only");
     if (N > BM && gemm_tc_pair_enabled() &&
         gemm_tc_pair(a, lda, w, ldw, expert_offsets, num_experts, bias, out, ldo, M, N, K, out_dtype, epilogue, stream))
         return true;
@@ -272,7 +272,7 @@ bool gemm_tc(const void* a, int lda, const void* w, int ldw, const int32_t* expe
     // (measured: 109 -> 95 us for the experts' down projection of a 2,048-token step).  The SwiGLU epilogue is
     // too long to run without the next tile's MMAs beside it (191 -> 239 us), so it keeps one weight tile and
     // two alternating accumulators, as the dense products do.
-    const int g = (expert_offsets != nullptr && (epilogue == EPI_STORE || epilogue == EPI_GELU)) ? 2 : 1;
+    const int g = (expert_offsets != nullptr && (epilogue == EPI_STORE || epilogue == EPI_GELU || epilogue == EPI_GELU_TANH)) ? 2 : 1;
     const int nx = (N + g * BM - 1) / (g * BM);
     DLM_CHECK((long long)nx * t_tiles < (1LL << 30), "gemm: too many tiles for one launch");
     const int total_tiles = nx * t_tiles;
@@ -284,6 +284,8 @@ bool gemm_tc(const void* a, int lda, const void* w, int ldw, const int32_t* expe
         case EPI_ADD: launch<G, EPI_ADD, float>(mw, ma, p, nx, total_tiles, stream); break;                 \
         case EPI_GELU: if (f32) launch<G, EPI_GELU, float>(mw, ma, p, nx, total_tiles, stream);             \
                        else launch<G, EPI_GELU, __nv_bfloat16>(mw, ma, p, nx, total_tiles, stream); break;  \
+        case EPI_GELU_TANH: if (f32) launch<G, EPI_GELU_TANH, float>(mw, ma, p, nx, total_tiles, stream);        \
+                       else launch<G, EPI_GELU_TANH, __nv_bfloat16>(mw, ma, p, nx, total_tiles, stream); break;  \
         default: if (f32) launch<G, EPI_SWIGLU, float>(mw, ma, p, nx, total_tiles, stream);                 \
                  else launch<G, EPI_SWIGLU, __nv_bfloat16>(mw, ma, p, nx, total_tiles, stream); break;      \
     }

@@ -66,7 +66,7 @@ __device__ __forceinline__ void epilogue_tile(const TcParams& p, float* st, uint
                                               int row_begin, int row_end, int hsel, int lane, bool vec_ok) {
     const int col = colw + lane;
     const bool col_ok = col < p.N;
-    const float bias = ((EPI == EPI_STORE || EPI == EPI_GELU) && p.bias != nullptr && col_ok) ? p.bias[col] : 0.f;
+    const float bias = ((EPI == EPI_STORE || EPI == EPI_GELU || EPI == EPI_GELU_TANH) && p.bias != nullptr && col_ok) ? p.bias[col] : 0.f;
 #pragma unroll 1
     for (int c0 = hsel * CH; c0 < n_mma; c0 += 2 * CH) {
         uint32_t v[CH];

@@ -327,6 +327,8 @@ bool gemm_tc_pair(const void* a, int lda, const void* w, int ldw, const int32_t*
         case EPI_ADD: launch<ST, AR, EPI_ADD, float>(mw, ma, p, nx, total_tiles, tt, stream); break;              \
         case EPI_GELU: if (f32) launch<ST, AR, EPI_GELU, float>(mw, ma, p, nx, total_tiles, tt, stream);          \
                        else launch<ST, AR, EPI_GELU, __nv_bfloat16>(mw, ma, p, nx, total_tiles, tt, stream); break; \
+        case EPI_GELU_TANH: if (f32) launch<ST, AR, EPI_GELU_TANH, float>(mw, ma, p, nx, total_tiles, tt, stream);     \
+                       else launch<ST, AR, EPI_GELU_TANH, __nv_bfloat16>(mw, ma, p, nx, total_tiles, tt, stream); break; \
         default: if (f32) launch<ST, AR, EPI_SWIGLU, float>(mw, ma, p, nx, total_tiles, tt, stream);              \
                  else launch<ST, AR, EPI_SWIGLU, __nv_bfloat16>(mw, ma, p, nx, total_tiles, tt, stream); break;   \
     }

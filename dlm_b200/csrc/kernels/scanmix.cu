@@ -5,6 +5,7 @@
 //     with the position, and the write of queries, keys and values in the layout of the attention kernels;
 //   * rotate_heads: rotary positions applied in place to 32-bit rows (two runs of heads, each with a factor);
 //   * branch_norm_add: resid += coef * sum_b rms_norm(branch_b) * w_b for one or two branch outputs;
+//   * rmsnorm_pair: two RMS norms of the same rows (one statistic, two weights);
 //   * concat_rows: [a | b] in the activation dtype (the input of a product that reads two residuals).
 //
 // Everything is computed in 32-bit whatever the activation dtype is; only what a kernel hands to a matrix product
@@ -23,15 +24,24 @@ __device__ __forceinline__ void copy4_async(float* dst_smem, const float* src) {
                  : "memory");
 }
 __device__ __forceinline__ void copies_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void copy16_async(float* dst_smem, const float* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst_smem)), "l"(src)
+                 : "memory");
+}
 template <int N> __device__ __forceinline__ void copies_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // ------------------------------------------------------------------ selective scan
 // A block owns (a run of `chans` channels, a request).  A channel's N states are shared by `parts` neighbouring
-// lanes, lane `part` keeps states part, part + parts, ... in registers (NPT of them); the sum over states meets
-// in a butterfly of shuffles (a fixed order).  Tokens come in tiles of TILE by asynchronous copies into one of
-// two buffers: per token B and C (N each, shared by all channels), and the block's x and raw dt.
+// lanes, lane `part` keeps states part, part + parts, ... in registers (NPT of them).  Tokens come in tiles of TILE
+// by asynchronous copies into a ring of buffers, three tiles ahead: per token B and C (N each, shared by all channels), and the
+// block's x, raw dt and z.  A tile is worked on in three phases: (1) all threads turn its raw step sizes into
+// dt = softplus(raw + bias) at once; (2) every lane walks the tile's tokens with its own states and leaves its part
+// of each token's sum over states in shared memory: a token's only dependence on the one before it is the state's
+// own multiply-add, so a full tile's walk is unrolled; (3) all threads add the parts of a (token, channel) in lane
+// order, add D x, apply the gate and store.  The decay exp(dt A) is 2^(dt A log2 e) with A log2 e kept in registers.
 constexpr int SCAN_THREADS = 128;
 constexpr int SCAN_TILE = 16;
+constexpr int SCAN_STAGES = 4;     // tiles asked for ahead of the one worked on: a tile's walk is shorter than a trip to memory
 
 template <int NPT, typename TOut>
 __global__ void __launch_bounds__(SCAN_THREADS)
@@ -39,78 +49,109 @@ selective_scan_kernel(const float* __restrict__ x, int ldx, const float* __restr
                       const float* __restrict__ bc, int ldbc, const float* __restrict__ z, int ldz,
                       const float* __restrict__ dt_bias, const float* __restrict__ A_log, const float* __restrict__ D,
                       float* state, const int32_t* __restrict__ cu_q, const int32_t* __restrict__ state_slot, TOut* out,
-                      int ldo, int inner, int N, int parts) {
+                      int ldo, int inner, int N, int parts, int wide) {
     dep_wait();          // nothing is read or written before the kernels before this one have ended
-    extern __shared__ __align__(16) float sm[];       // [2][TILE][2 N + 2 chans]: B, C, x, dt
+    extern __shared__ __align__(16) float sm[];       // [STAGES][TILE][2 N + 3 chans]: B, C, x, dt, z;  then [TILE][chans][parts + 1]
     const int chans = SCAN_THREADS / parts;
     const int part = threadIdx.x % parts, col = threadIdx.x / parts;
     const int c0 = blockIdx.x * chans, c = c0 + col;
     const int r = blockIdx.y;
     const bool live = c < inner;
-    const int rl = 2 * N + 2 * chans;
+    const int rl = 2 * N + 3 * chans;
+    // a channel's parts lie side by side, channels parts + 1 apart: lanes that add up different channels' parts read
+    // different banks
+    float* ps = sm + SCAN_STAGES * (size_t)SCAN_TILE * rl;
+    const int ps_ld = chans * (parts + 1);
+    float* mine = ps + col * (parts + 1) + part;
     float* st = state + ((long long)state_slot[r] * inner + (live ? c : 0)) * N;
-    float s[NPT], a[NPT];
+    float s[NPT], a2[NPT];
 #pragma unroll
     for (int i = 0; i < NPT; ++i) {
         const int n = part + parts * i;
         const bool ok = live && n < N;
         s[i] = ok ? st[n] : 0.f;
-        a[i] = ok ? -expf(A_log[(long long)c * N + n]) : 0.f;
+        a2[i] = ok ? -expf(A_log[(long long)c * N + n]) * 1.4426950408889634f : 0.f;
     }
-    const float dcoef = live ? D[c] : 0.f, bias = live ? dt_bias[c] : 0.f;
     const int t0 = cu_q[r], t1 = cu_q[r + 1];
     const int n_tiles = (t1 - t0 + SCAN_TILE - 1) / SCAN_TILE;
     const int nch = min(chans, inner - c0);
-    auto fetch = [&](int k) {
-        float* buf = sm + (size_t)(k & 1) * SCAN_TILE * rl;
+    // `wide`: every run of a token's inputs starts on a 16-byte boundary and is a multiple of four floats
+    auto fetch = [&](int k) {             // (a tile beyond the last: an empty group, so that the count of groups holds)
+        float* buf = sm + (size_t)(k % SCAN_STAGES) * SCAN_TILE * rl;
         const int first = t0 + k * SCAN_TILE, n = min(SCAN_TILE, t1 - first);
         const int lane = threadIdx.x & 31, nwarp = SCAN_THREADS >> 5;
         for (int tok = threadIdx.x >> 5; tok < n; tok += nwarp) {
-            const float* src_bc = bc + (long long)(first + tok) * ldbc;
+            const long long t = first + tok;
+            const float* src_bc = bc + t * ldbc;
+            const float* src_x = x + t * ldx + c0;
+            const float* src_dt = dt_raw + t * lddt + c0;
+            const float* src_z = z + t * ldz + c0;
             float* dst = buf + (size_t)tok * rl;
-            for (int i = lane; i < 2 * N; i += 32) copy4_async(dst + i, src_bc + i);
-            const float* src_x = x + (long long)(first + tok) * ldx + c0;
-            const float* src_dt = dt_raw + (long long)(first + tok) * lddt + c0;
-            for (int i = lane; i < nch; i += 32) {
-                copy4_async(dst + 2 * N + i, src_x + i);
-                copy4_async(dst + 2 * N + chans + i, src_dt + i);
+            if (wide) {
+                for (int i = 4 * lane; i < 2 * N; i += 128) copy16_async(dst + i, src_bc + i);
+                for (int i = 4 * lane; i < nch; i += 128) {
+                    copy16_async(dst + 2 * N + i, src_x + i);
+                    copy16_async(dst + 2 * N + chans + i, src_dt + i);
+                    copy16_async(dst + 2 * N + 2 * chans + i, src_z + i);
+                }
+            } else {
+                for (int i = lane; i < 2 * N; i += 32) copy4_async(dst + i, src_bc + i);
+                for (int i = lane; i < nch; i += 32) {
+                    copy4_async(dst + 2 * N + i, src_x + i);
+                    copy4_async(dst + 2 * N + chans + i, src_dt + i);
+                    copy4_async(dst + 2 * N + 2 * chans + i, src_z + i);
+                }
             }
         }
         copies_commit();
     };
-    if (n_tiles > 0) fetch(0);
+    // one token of the walk: the lane's states move on, its part of the token's sum goes to shared memory
+    auto one = [&](const float* row, float* dst) {
+        const float dt = row[2 * N + chans + col];
+        const float dx = dt * row[2 * N + col];
+        float sum = 0.f;
+#pragma unroll
+        for (int i = 0; i < NPT; ++i) {
+            const int n_i = part + parts * i;
+            if (n_i < N) {
+                s[i] = fmaf(exp2f(dt * a2[i]), s[i], dx * row[n_i]);
+                sum = fmaf(s[i], row[N + n_i], sum);
+            }
+        }
+        *dst = sum;
+    };
+    for (int k = 0; k < SCAN_STAGES - 1; ++k) fetch(k);
     for (int k = 0; k < n_tiles; ++k) {
-        if (k + 1 < n_tiles) {
-            fetch(k + 1);
-            copies_wait<1>();
-        } else {
-            copies_wait<0>();
+        fetch(k + SCAN_STAGES - 1);          // into the buffer of tile k - 1, which the barrier below the last phase freed
+        copies_wait<SCAN_STAGES - 1>();
+        __syncthreads();
+        float* buf = sm + (size_t)(k % SCAN_STAGES) * SCAN_TILE * rl;
+        const int first = t0 + k * SCAN_TILE, n = min(SCAN_TILE, t1 - first);
+        for (int idx = threadIdx.x; idx < n * nch; idx += SCAN_THREADS) {
+            const int tok = idx / nch, ch = idx - tok * nch;
+            float* p = buf + (size_t)tok * rl + 2 * N + chans + ch;
+            *p = softplus_f(*p + dt_bias[c0 + ch]);
         }
         __syncthreads();
-        const float* buf = sm + (size_t)(k & 1) * SCAN_TILE * rl;
-        const int first = t0 + k * SCAN_TILE, n = min(SCAN_TILE, t1 - first);
-        for (int tok = 0; tok < n; ++tok) {
-            const float* row = buf + (size_t)tok * rl;
-            const float xv = live ? row[2 * N + col] : 0.f;
-            const float dt = live ? softplus_f(row[2 * N + chans + col] + bias) : 0.f;
-            const float dx = dt * xv;
-            float acc = 0.f;
+        if (live) {
+            if (n == SCAN_TILE) {
 #pragma unroll
-            for (int i = 0; i < NPT; ++i) {
-                const int n_i = part + parts * i;
-                if (n_i < N) {
-                    s[i] = fmaf(expf(dt * a[i]), s[i], dx * row[n_i]);
-                    acc = fmaf(s[i], row[N + n_i], acc);
-                }
-            }
-            for (int o = parts >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-            if (live && part == 0) {
-                const long long t = first + tok;
-                const float y = fmaf(dcoef, xv, acc);
-                out[t * ldo + c] = from_f32<TOut>(y * silu_f(z[t * ldz + c]));
+                for (int tok = 0; tok < SCAN_TILE; ++tok) one(buf + (size_t)tok * rl, mine + tok * ps_ld);
+            } else {
+                for (int tok = 0; tok < n; ++tok) one(buf + (size_t)tok * rl, mine + tok * ps_ld);
             }
         }
-        __syncthreads();                     // the buffer may be filled again
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < n * nch; idx += SCAN_THREADS) {
+            const int tok = idx / nch, ch = idx - tok * nch;
+            const float* row = buf + (size_t)tok * rl;
+            const float* pp = ps + tok * ps_ld + ch * (parts + 1);
+            float v = 0.f;
+            for (int p = 0; p < parts; ++p) v += pp[p];
+            const float y = fmaf(D[c0 + ch], row[2 * N + ch], v);
+            out[(long long)(first + tok) * ldo + c0 + ch] = from_f32<TOut>(y * silu_f(row[2 * N + 2 * chans + ch]));
+        }
+        __syncthreads();                     // this tile's buffer and the sums may be written again
     }
 #pragma unroll
     for (int i = 0; i < NPT; ++i) {
@@ -247,6 +288,26 @@ __global__ void branch_norm_add_kernel(float* resid, const float* a, const float
     }
 }
 
+// ------------------------------------------------------------ two norms of the same rows
+// One block a row: out_a = x / rms(x) * wa, out_b = x / rms(x) * wb (one statistic, two weights).
+template <typename T>
+__global__ void rmsnorm_pair_kernel(const float* x, const float* __restrict__ wa, const float* __restrict__ wb, T* out_a,
+                                    T* out_b, int H, float eps) {
+    __shared__ float s_part[32];
+    dep_wait();
+    dep_launch_next();
+    const long long t = blockIdx.x;
+    const float* row = x + t * H;
+    float part = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) part = fmaf(row[i], row[i], part);
+    const float inv = 1.0f / sqrtf(block_sum(part, s_part) / (float)H + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = row[i] * inv;
+        out_a[t * H + i] = from_f32<T>(v * wa[i]);
+        out_b[t * H + i] = from_f32<T>(v * wb[i]);
+    }
+}
+
 // ------------------------------------------------------------------ two rows side by side
 template <typename T>
 __global__ void concat_rows_kernel(const float* a, const float* b, T* out, int H) {
@@ -267,13 +328,20 @@ void selective_scan(const float* x, int ldx, const float* dt_raw, int lddt, cons
                     int out_dtype, cudaStream_t stream) {
     if (R <= 0 || inner <= 0) return;
     DLM_CHECK(N >= 1 && N <= 256, "selective_scan: state size 1..256");
-    // few states a lane, so that a channel spreads over lanes and a prompt of one request still makes many blocks
+    // few states a lane, so that a channel spreads over lanes; fewer still while the launch would not fill the
+    // machine three times over (a prompt of one request is walked by inner / chans blocks)
     int parts = 1;
     while (parts < 32 && (N + parts - 1) / parts > 4) parts <<= 1;
+    while (parts < 32 && (N + parts - 1) / parts > 1 &&
+           (long long)((inner + SCAN_THREADS / parts - 1) / (SCAN_THREADS / parts)) * R < 3LL * sm_count())
+        parts <<= 1;
     const int per = (N + parts - 1) / parts;
     const int chans = SCAN_THREADS / parts;
     const dim3 grid((inner + chans - 1) / chans, R);
-    const size_t smem = 2 * (size_t)SCAN_TILE * (2 * N + 2 * chans) * sizeof(float);
+    const size_t smem = (SCAN_STAGES * (size_t)SCAN_TILE * (2 * N + 3 * chans) + (size_t)SCAN_TILE * (SCAN_THREADS + chans)) * sizeof(float);
+    const int wide = (((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dt_raw) | reinterpret_cast<uintptr_t>(bc) |
+                        reinterpret_cast<uintptr_t>(z)) & 15) == 0 && ldx % 4 == 0 && lddt % 4 == 0 && ldbc % 4 == 0 &&
+                      ldz % 4 == 0 && N % 2 == 0 && chans % 4 == 0 && inner % 4 == 0) ? 1 : 0;
 #define DLM_SEL(NPT, TOUT)                                                                                           \
     do {                                                                                                             \
         if (smem > 48 * 1024)                                                                                        \
@@ -281,7 +349,7 @@ void selective_scan(const float* x, int ldx, const float* dt_raw, int lddt, cons
                                  (int)smem);                                                                         \
         selective_scan_kernel<NPT, TOUT><<<grid, SCAN_THREADS, smem, stream>>>(                                      \
             x, ldx, dt_raw, lddt, bc, ldbc, z, ldz, dt_bias, A_log, D, state, cu_q, state_slot,                      \
-            static_cast<TOUT*>(out), ldo, inner, N, parts);                                                          \
+            static_cast<TOUT*>(out), ldo, inner, N, parts, wide);                                                       \
     } while (0)
 #define DLM_SEL_T(NPT)                                                                 \
     do {                                                                               \
@@ -333,6 +401,19 @@ void branch_norm_add(float* resid, const float* a, const float* wa, const float*
     DLM_CHECK(a != nullptr && wa != nullptr && (b == nullptr || wb != nullptr), "branch_norm_add: a branch needs its weight");
     launch_dep(branch_norm_add_kernel, dim3(T), dim3(H >= 1024 ? 256 : 128), 0, stream, resid, a, wa, b, wb, eps, coef, H);
     check_launch("branch_norm_add");
+}
+
+void rmsnorm_pair(const float* x, const float* wa, const float* wb, void* out_a, void* out_b, int T, int H, float eps,
+                  int out_dtype, cudaStream_t stream) {
+    if (T <= 0) return;
+    const int threads = H >= 1024 ? 256 : 128;
+    if (out_dtype == F32)
+        launch_dep(rmsnorm_pair_kernel<float>, dim3(T), dim3(threads), 0, stream, x, wa, wb, static_cast<float*>(out_a),
+                   static_cast<float*>(out_b), H, eps);
+    else
+        launch_dep(rmsnorm_pair_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, x, wa, wb,
+                   static_cast<__nv_bfloat16*>(out_a), static_cast<__nv_bfloat16*>(out_b), H, eps);
+    check_launch("rmsnorm_pair");
 }
 
 void concat_rows(const float* a, const float* b, void* out, int T, int H, int out_dtype, cudaStream_t stream) {

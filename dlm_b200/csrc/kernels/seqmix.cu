@@ -304,6 +304,8 @@ template <int N> __device__ __forceinline__ void copies_wait() { asm volatile("c
 // nothing waits for memory.
 // VEC (N a multiple of 4): a lane's rows come in fours, 4 part + e + 4 parts q, so that B and C are read with
 // 16-byte shared loads that neighbouring lanes take from neighbouring addresses.
+constexpr int SSM_STAGES = 4;
+
 template <int NPT, bool VEC>
 __global__ void ssm_scan_kernel(const float* __restrict__ xbc, int ldx, const float* __restrict__ dt_raw, int lddt,
                                 const float* __restrict__ dt_bias, const float* __restrict__ A_log,
@@ -313,7 +315,7 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, int ldx, const fl
     dep_wait();          // nothing is read or written before the kernels before this one have ended
     // (a long kernel, launched in the ordinary way: its blocks are placed when the machine is free, and the
     // kernel after it is let in only when it ends)
-    extern __shared__ __align__(16) float sm[];            // [2][tile][2 N + cols + 2]: B, C, x, dt, decay
+    extern __shared__ __align__(16) float sm[];            // [SSM_STAGES][tile][2 N + cols + 2]: B, C, x, dt, decay
     const int h = blockIdx.x, r = blockIdx.y;
     const int cols = blockDim.x / parts;
     const int part = threadIdx.x % parts;
@@ -339,8 +341,8 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, int ldx, const fl
     const int t0 = cu_q[r], t1 = cu_q[r + 1];
     const int n_tiles = (t1 - t0 + tile - 1) / tile;
     // a warp fetches a token at a time; `wide`: every run starts on a 16-byte boundary and is a multiple of four
-    auto fetch = [&](int k) {
-        float* buf = sm + (size_t)(k & 1) * tile * rl;
+    auto fetch = [&](int k) {             // (a tile beyond the last: an empty group, so that the count of groups holds)
+        float* buf = sm + (size_t)(k % SSM_STAGES) * tile * rl;
         const int first = t0 + k * tile, n = min(tile, t1 - first);
         const int lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
         for (int tok = threadIdx.x >> 5; tok < n; tok += nwarp) {
@@ -367,16 +369,13 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, int ldx, const fl
         }
         copies_commit();
     };
-    if (n_tiles > 0) fetch(0);
+    // tiles are asked for three ahead of the one worked on: a tile's walk is shorter than a trip to memory
+    for (int k = 0; k < SSM_STAGES - 1; ++k) fetch(k);
     for (int k = 0; k < n_tiles; ++k) {
-        if (k + 1 < n_tiles) {
-            fetch(k + 1);
-            copies_wait<1>();
-        } else {
-            copies_wait<0>();
-        }
+        fetch(k + SSM_STAGES - 1);           // into the buffer of tile k - 1, freed by the barrier that ended its walk
+        copies_wait<SSM_STAGES - 1>();
         __syncthreads();
-        float* buf = sm + (size_t)(k & 1) * tile * rl;
+        float* buf = sm + (size_t)(k % SSM_STAGES) * tile * rl;
         const int first = t0 + k * tile, n = min(tile, t1 - first);
         if (threadIdx.x < n) {
             float* row = buf + (size_t)threadIdx.x * rl;
@@ -385,6 +384,9 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, int ldx, const fl
             row[2 * N + cols + 1] = fixed ? decay_h : expf(a * dt);
         }
         __syncthreads();
+        // (unrolled: a token depends on the one before it through the state's own multiply-add only, so the sums
+        // and shuffles of neighbouring tokens overlap)
+#pragma unroll 4
         for (int tok = 0; tok < n; ++tok) {
             const float* row = buf + (size_t)tok * rl;
             const float dt = row[2 * N + cols], decay = row[2 * N + cols + 1];
@@ -745,10 +747,13 @@ void ssm_scan(const float* xbc, int ldx, const float* dt_raw, int lddt, const fl
     int parts, cols, chunks;
     const bool vec = N % 4 == 0;
     scan_layout(N, P, 8, &parts, &cols, &chunks, vec);   // few rows a lane: many lanes a column, many warps an SM
+    // a launch that leaves multiprocessors idle (a prompt of one request, few heads): half the rows a lane, twice the blocks
+    if (vec && (long long)heads * R * chunks < sm_count()) scan_layout(N, P, 4, &parts, &cols, &chunks, vec);
     const int per = vec ? 4 * ((N / 4 + parts - 1) / parts) : (N + parts - 1) / parts;
     const int rl = (2 * N + cols + 2 + 3) & ~3;
-    const int tile = scan_tile(rl);
-    const size_t smem = 2 * (size_t)tile * rl * sizeof(float);
+    int tile = scan_tile(rl);
+    while (tile > 1 && SSM_STAGES * (size_t)tile * rl * sizeof(float) > 96 * 1024) tile /= 2;
+    const size_t smem = SSM_STAGES * (size_t)tile * rl * sizeof(float);
     DLM_CHECK(smem <= 200 * 1024, "ssm_scan: a token's inputs do not fit in shared memory");
     const dim3 grid(heads, R, chunks);
     // 16-byte copies: every run of a token's inputs starts on a 16-byte boundary and is a multiple of four floats

@@ -272,6 +272,16 @@ class NativeOps:
         self.launches += 1
         self.k.branch_norm_add(_p(resid), _p(a), _p(wa), _p(b), _p(wb), float(eps), float(coef), T, H, self._stream())
 
+    def rmsnorm_pair(self, x, wa, wb, eps, out_dtype):
+        """Two RMS norms of the same 32-bit rows with one statistic: ``(x / rms(x) * wa, x / rms(x) * wb)``."""
+        T, H = x.shape
+        assert x.dtype == torch.float32 and x.is_contiguous() and wa.shape == (H,) and wb.shape == (H,)
+        a = torch.empty((T, H), dtype=out_dtype, device=x.device)
+        b = torch.empty((T, H), dtype=out_dtype, device=x.device)
+        self.launches += 1
+        self.k.rmsnorm_pair(_p(x), _p(wa), _p(wb), _p(a), _p(b), T, H, float(eps), _dt(out_dtype), self._stream())
+        return a, b
+
     def concat_rows(self, a, b, out_dtype):
         """``[a | b]`` in ``out_dtype`` (a, b 32-bit ``[T, H]``)."""
         T, H = a.shape
@@ -378,13 +388,14 @@ class NativeOps:
         self._gemm(a, w, resid, M, N, K, self.k.EPI_ADD)
 
     def linear_act(self, a, w, act):
-        """``act(a · w^T)`` in the activation dtype; ``act`` as in ``activation``.  The exact gelu is the product's
-        epilogue, the other activations a kernel behind a 32-bit product."""
+        """``act(a · w^T)`` in the activation dtype; ``act`` as in ``activation``.  Both forms of gelu are an epilogue
+        of the product, the other activations a kernel behind a 32-bit product."""
         (M, K), N = a.shape, w.shape[0]
         assert w.shape[1] == K and a.dtype == w.dtype
-        if act == "gelu":
+        epi = {"gelu": self.k.EPI_GELU, "gelu_tanh": self.k.EPI_GELU_TANH}.get(act)
+        if epi is not None:
             out = torch.empty((M, N), dtype=a.dtype, device=a.device)
-            self._gemm(a, w, out, M, N, K, self.k.EPI_GELU)
+            self._gemm(a, w, out, M, N, K, epi)
             return out
         return self.activation(self.linear(a, w, None, torch.float32), act, a.dtype)
 

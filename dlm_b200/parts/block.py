@@ -74,9 +74,16 @@ class ParallelBlock(PreNormBlock):
 
     def forward(self, resid, ctx: StepContext, call: int):
         rt = ctx.rt
-        h1 = self.norm1.forward(resid, rt)
-        if self.ffn is not None:
-            self.ffn.forward(self.norm2.forward(resid, rt), resid, ctx, pre_norm=self.norm2)
+        if self.ffn is None:
+            self.mixer.forward(self.norm1.forward(resid, rt), resid, ctx, call)
+            return
+        a, b = self.norm1.fusable_rms(), self.norm2.fusable_rms()
+        if a is not None and b is not None and a[1] == b[1]:
+            # two RMS norms of the same rows: one statistic, one pass
+            h1, h2 = rt.ops.rmsnorm_pair(resid, a[0], b[0], a[1], rt.dtype)
+        else:
+            h1, h2 = self.norm1.forward(resid, rt), self.norm2.forward(resid, rt)
+        self.ffn.forward(h2, resid, ctx, pre_norm=self.norm2)
         self.mixer.forward(h1, resid, ctx, call)
 
 

@@ -40,7 +40,7 @@ class DenseSwiGLU(FeedForward):
 
 class DenseActMLP(FeedForward):
     """``resid += down · act(up · h)`` without biases; ``activation``: "gelu_tanh" (the tanh form), "gelu" (the exact
-    form) or "silu".  The exact gelu sits in the first product's epilogue; the others are a kernel behind it."""
+    form) or "silu".  Either gelu sits in the first product's epilogue; silu is a kernel behind it."""
 
     def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "gelu_tanh"):
         self.hidden, self.inter = int(hidden_size), int(intermediate_size)

@@ -276,11 +276,13 @@ class ParallelMixers(Mixer):
 
     def forward(self, h, resid, ctx: StepContext, call: int):
         ops = ctx.rt.ops
-        outs = []
-        for part in self.parts:
-            y = torch.zeros_like(resid)
-            part.forward(h, y, ctx, call)
-            outs.append(y)
+        outs = [torch.zeros_like(resid), torch.zeros_like(resid)]
+        # neither mixer needs anything of the other: in a small step the second runs beside the first
+        branch = ops.branch(h.shape[0])
+        with branch:
+            self.parts[1].forward(h, outs[1], ctx, call)
+        self.parts[0].forward(h, outs[0], ctx, call)
+        branch.join()
         ops.branch_norm_add(resid, outs[0], self.w_out[0], outs[1], self.w_out[1], self.eps, self.coef)
 
 

@@ -182,6 +182,10 @@ class PlainOps:
             v = v + b / torch.sqrt((b * b).mean(-1, keepdim=True) + eps) * wb
         resid += coef * v
 
+    def rmsnorm_pair(self, x, wa, wb, eps, out_dtype):
+        v = x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)
+        return (v * wa).to(out_dtype), (v * wb).to(out_dtype)
+
     def concat_rows(self, a, b, out_dtype):
         return torch.cat([a, b], dim=-1).to(out_dtype)
 
