@@ -185,12 +185,24 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
             // scale (to base 2), mask where needed, running maximum
             float mx_a = m_a, mx_b = m_b;
             const bool all_visible = j0 + BKV - 1 <= w_lo && (window <= 0 || w_hi - j0 < window);
+            // the distance term slope * (key - p) of an entry: a part per row and tile, a part per column of the tile
+            const float far_a = slope2 * (float)(j0 + 2 * t - pa), far_b = slope2 * (float)(j0 + 2 * t - pb);
             if (all_visible && slope2 == 0.f) {
 #pragma unroll
                 for (int j = 0; j < BKV / 8; ++j) {
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
                         const float v = s[j][c] * scale_log2;
+                        s[j][c] = v;
+                        if (c < 2) mx_a = fmaxf(mx_a, v); else mx_b = fmaxf(mx_b, v);
+                    }
+                }
+            } else if (all_visible) {
+#pragma unroll
+                for (int j = 0; j < BKV / 8; ++j) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const float v = fmaf(s[j][c], scale_log2, fmaf(slope2, (float)(j * 8 + (c & 1)), c < 2 ? far_a : far_b));
                         s[j][c] = v;
                         if (c < 2) mx_a = fmaxf(mx_a, v); else mx_b = fmaxf(mx_b, v);
                     }
@@ -203,7 +215,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
                         const int key = j0 + j * 8 + 2 * t + (c & 1);
                         const int p = (c < 2) ? pa : pb;
                         const bool vis = key <= p && (window <= 0 || p - key < window);
-                        const float v = vis ? s[j][c] * scale_log2 - slope2 * (float)(p - key) : -INFINITY;
+                        const float v = vis ? fmaf(s[j][c], scale_log2, fmaf(slope2, (float)(j * 8 + (c & 1)), c < 2 ? far_a : far_b))
+                                            : -INFINITY;
                         s[j][c] = v;
                         if (c < 2) mx_a = fmaxf(mx_a, v); else mx_b = fmaxf(mx_b, v);
                     }
