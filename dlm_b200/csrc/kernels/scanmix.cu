@@ -329,7 +329,9 @@ void selective_scan(const float* x, int ldx, const float* dt_raw, int lddt, cons
     if (R <= 0 || inner <= 0) return;
     DLM_CHECK(N >= 1 && N <= 256, "selective_scan: state size 1..256");
     // few states a lane, so that a channel spreads over lanes; fewer still while the launch would not fill the
-    // machine three times over (a prompt of one request is walked by inner / chans blocks)
+    // machine three times over (a prompt of one request is walked by inner / chans blocks).  Measured on a prompt of
+    // 2,048 tokens, 4,096 channels of 16 states: 2 / 4 / 8 / 16 lanes a channel take 1,446 / 789 / 597 / 495 us: the
+    // walk is a chain of dependent steps per lane, and what shortens a lane's chain shortens the kernel
     int parts = 1;
     while (parts < 32 && (N + parts - 1) / parts > 4) parts <<= 1;
     while (parts < 32 && (N + parts - 1) / parts > 1 &&
