@@ -36,7 +36,8 @@ class ZasazenConfig:
     embedding_scale: float = 1.0
     norm_eps: float = 1e-5
     loop: dict[str, int] | None = None       # {"start", "stop", "times"}
-    max_positions: int = 1 << 20             # the design has no table of positions: any length the cache holds
+    max_positions: int = 32768               # the design has no table of positions; this is the context an engine is
+                                             # made for when its caller names none (the key `max_positions` overrides it)
     eos_token_ids: list[int] = field(default_factory=list)
 
     architecture = "Zasazen"
@@ -72,7 +73,7 @@ class ZasazenConfig:
                   layers=copy.deepcopy(raw["layers"]),
                   embedding_scale=as_float((raw.get("embedding") or {}).get("scale", 1.0), "embedding.scale"),
                   norm_eps=as_float(_section(raw, "norm").get("eps", 1e-5), "norm.eps"), loop=loop,
-                  max_positions=as_int(raw.get("max_positions", 1 << 20), "max_positions", minimum=1))
+                  max_positions=as_int(raw.get("max_positions", 32768), "max_positions", minimum=1))
         cfg.validate()
         return cfg
 
@@ -134,6 +135,6 @@ class ZasazenConfig:
                "layers": copy.deepcopy(self.layers)}
         if self.loop is not None:
             out["loop"] = dict(self.loop)
-        if self.max_positions != 1 << 20:
+        if self.max_positions != 32768:
             out["max_positions"] = self.max_positions
         return out

@@ -40,7 +40,7 @@ template <int N> __device__ __forceinline__ void copies_wait() { asm volatile("c
 // own multiply-add, so a full tile's walk is unrolled; (3) all threads add the parts of a (token, channel) in lane
 // order, add D x, apply the gate and store.  The decay exp(dt A) is 2^(dt A log2 e) with A log2 e kept in registers.
 constexpr int SCAN_THREADS = 128;
-constexpr int SCAN_TILE = 16;
+constexpr int SCAN_TILE = 32;
 constexpr int SCAN_STAGES = 4;     // tiles asked for ahead of the one worked on: a tile's walk is shorter than a trip to memory
 
 template <int NPT, typename TOut>

@@ -60,7 +60,7 @@ def randn(*shape, seed=0, std=1.0):
 # ============================================================== kernels alone
 @pytest.mark.parametrize("inner,N", [(70, 5), (256, 16), (96, 40), (33, 1), (64, 130)])
 def test_selective_scan_in_portions_with_slots_used_again(ops, inner, N):
-    """Two requests fed in portions (1 to 40 tokens, past the kernel's tile of 16) beside each other: every output
+    """Two requests fed in portions (1 to 273 tokens, within and past the kernel's tile) beside each other: every output
     equals the scan over the whole sequence; the state of a slot that is zeroed starts a new sequence; a write of
     300 tokens ago is still in the state when the decay is slow."""
     ref = PlainOps()
